@@ -30,7 +30,7 @@ fi
 # profiler passes last: numbers printed under ncu are never bench values
 ncu --metrics gpu__time_duration.sum --clock-control none -c 400 --csv --log-file $OUT/${TAG}_launches_default.csv \
     python bench.py --steps 2 --warmup 1 > $OUT/${TAG}_ncu_launches.log 2>&1
-ncu --set full --clock-control none --import-source on -k regex:decode_persistent -c 1 -o $OUT/${TAG}_persistent_full -f \
+ncu --set full --clock-control none -k regex:decode_persistent -c 1 -o $OUT/${TAG}_persistent_full -f \
     python bench.py --steps 2 --warmup 1 > $OUT/${TAG}_ncu_full.log 2>&1
 ncu -i $OUT/${TAG}_persistent_full.ncu-rep --page raw --csv > $OUT/${TAG}_persistent_full_raw.csv 2>/dev/null
 ls -la $OUT | tail -30
