@@ -1,4 +1,4 @@
-// Layered decoders (FL_ARCH_NIFUNEX, FL_ARCH_ROFETAR): weight layout + ingest, pooled cache (pages of latents or keys | values +
+// Layered decoders (FL_ARCH_NIFUNEX, FL_ARCH_ROFETAR, FL_ARCH_TOZARAX): weight layout + ingest, pooled cache (pages of latents or keys | values +
 // recurrent-state slots), and the step function for mixed batches (portions of prompts beside single decoded tokens).
 #include <cmath>
 #include <map>
@@ -47,9 +47,12 @@ struct LayeredRoutes {
 static std::map<const LayeredModel*, LayeredRoutes> g_routes;      // built with the model, dropped at finalize
 static std::mutex g_routes_mu;
 
-static void check_layer(const LayeredModel& m, int i, const fl_layer_desc& d) {
-    const std::string at = "layer " + std::to_string(i) + ": ";
+static void check_mixer(const LayeredModel& m, int i, const fl_layer_desc& d, bool second) {
+    const std::string at = "layer " + std::to_string(i) + (second ? " (second mixer): " : ": ");
     FL_CHECK(d.heads >= 1 && (d.dim >= 1 || d.mixer == FL_MIXER_MAMBA2) && d.vdim >= 1, FL_ERR_INVALID, at + "heads / dim / vdim must be positive");
+    if (second || d.beside)
+        FL_CHECK((d.mixer == FL_MIXER_ATTN || d.mixer == FL_MIXER_DELTA) && d.kv_from < 0, FL_ERR_UNSUPPORTED,
+                 at + "mixers side by side: attention or delta rule, each with its own cache");
     if (d.mixer == FL_MIXER_GLA) {
         FL_CHECK(d.decay_rank >= 1 && d.decay_rank <= 4096 && d.tau > 0.f, FL_ERR_INVALID, at + "bad decay rank / tau");
         FL_CHECK(d.dim <= 256, FL_ERR_UNSUPPORTED, at + "gated linear attention: at most 256 key channels per head");
@@ -92,14 +95,28 @@ static void check_layer(const LayeredModel& m, int i, const fl_layer_desc& d) {
     } else {
         FL_CHECK(false, FL_ERR_INVALID, at + "unknown mixer");
     }
-    FL_CHECK(d.ffn_act == FL_ACT_SWISH_CLAMP || d.ffn_act == FL_ACT_GELU_TANH, FL_ERR_INVALID, at + "unknown feed-forward activation");
-    FL_CHECK(d.ffn != FL_FFN_MOE || (d.ffn_act == FL_ACT_SWISH_CLAMP && !d.ffn_bias), FL_ERR_UNSUPPORTED,
-             at + "experts use the clamped activation without biases");
+}
+
+static void check_layer(const LayeredModel& m, int i, const fl_layer_desc& d) {
+    const std::string at = "layer " + std::to_string(i) + ": ";
+    check_mixer(m, i, d, false);
+    FL_CHECK(d.ffn_act == FL_ACT_SWISH_CLAMP || d.ffn_act == FL_ACT_GELU_TANH || d.ffn_act == FL_ACT_RELU2, FL_ERR_INVALID,
+             at + "unknown feed-forward activation");
+    FL_CHECK(d.ffn != FL_FFN_MOE || ((d.ffn_act == FL_ACT_SWISH_CLAMP || d.ffn_act == FL_ACT_RELU2) && !d.ffn_bias), FL_ERR_UNSUPPORTED,
+             at + "experts use the clamped or the squared-relu activation, without biases");
+    FL_CHECK(!(d.ffn_act == FL_ACT_RELU2 && d.ffn_bias), FL_ERR_UNSUPPORTED, at + "the squared-relu feed-forward has no biases");
     if (d.ffn == FL_FFN_DENSE) {
         FL_CHECK(d.ff >= 1, FL_ERR_INVALID, at + "ff must be positive");
     } else if (d.ffn == FL_FFN_MOE) {
         FL_CHECK(d.ff >= 1 && d.experts >= 1 && d.experts <= 1024 && d.top >= 1 && d.top <= d.experts && d.shared_ff >= 0, FL_ERR_INVALID,
                  at + "bad expert counts");
+        FL_CHECK(d.router == FL_ROUTER_SOFTMAX || d.router == FL_ROUTER_SIGMOID_GROUPS, FL_ERR_INVALID, at + "unknown router");
+        if (d.router == FL_ROUTER_SIGMOID_GROUPS) {
+            FL_CHECK(d.route_groups >= 1 && d.experts % d.route_groups == 0 && d.route_keep >= 1 && d.route_keep <= d.route_groups, FL_ERR_INVALID,
+                     at + "experts must divide into route_groups groups of which 1..route_groups are kept");
+            FL_CHECK(d.top <= d.route_keep * (d.experts / d.route_groups), FL_ERR_INVALID, at + "the kept groups hold fewer than `top` experts");
+            FL_CHECK(d.shared_ff == 0, FL_ERR_UNSUPPORTED, at + "the sigmoid router has no shared expert");
+        }
     } else {
         FL_CHECK(d.ffn == FL_FFN_NONE, FL_ERR_INVALID, at + "unknown feed-forward kind");
     }
@@ -107,9 +124,13 @@ static void check_layer(const LayeredModel& m, int i, const fl_layer_desc& d) {
 
 void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
     const fl_stack_config& c = m.cfg;
-    FL_CHECK(c.arch == FL_ARCH_NIFUNEX || c.arch == FL_ARCH_ROFETAR, FL_ERR_INVALID, "layered models: unknown arch");
+    FL_CHECK(c.arch == FL_ARCH_NIFUNEX || c.arch == FL_ARCH_ROFETAR || c.arch == FL_ARCH_TOZARAX, FL_ERR_INVALID, "layered models: unknown arch");
     FL_CHECK(c.vocab >= 1 && c.width >= 1 && c.n_layers >= 1 && c.n_layers <= 4096, FL_ERR_INVALID, "layered models: sizes must be positive");
     FL_CHECK(c.compute_dtype == FL_DTYPE_BF16 || c.compute_dtype == FL_DTYPE_F32, FL_ERR_INVALID, "compute_dtype must be bf16 or f32");
+    FL_CHECK(!(c.no_pre_norm && c.no_post_norm), FL_ERR_INVALID, "a stack norms its sublayers' inputs, their outputs, or both");
+    FL_CHECK(c.max_positions >= 0 && c.canon_taps >= 0 && c.canon_taps <= kMaxTaps, FL_ERR_INVALID, "bad position table / input convolution size");
+    FL_CHECK(c.no_post_norm || !(c.gated_residual || c.depth_avg), FL_ERR_UNSUPPORTED,
+             "gated contributions and the depth average are built for stacks whose sublayer results join the stream un-normed");
     m.W = c.width; m.V = c.vocab; m.L = c.n_layers; m.f32 = c.compute_dtype == FL_DTYPE_F32;
     m.layers.resize(m.L);
     struct Reg { void** pp; size_t bytes; };
@@ -117,45 +138,43 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
     auto reg = [&](auto** pp, size_t bytes) { regs.push_back({(void**)pp, bytes}); };
     const size_t W = m.W;
     reg(&m.embed, (size_t)m.V * W * 2); reg(&m.head, (size_t)m.V * W * 2); reg(&m.final_norm, W * 4);
-    for (int i = 0; i < m.L; ++i) {
-        LayeredLayerW& lw = m.layers[i];
-        lw.d = descs[i];
+    if (c.max_positions > 0) reg(&m.pos, (size_t)c.max_positions * W * 2);
+    auto pad8 = [](int n) { return (n + 7) / 8 * 8; };
+    // one mixer: its rows inside the layer's stacked input matrix start at `base`; registers its side tables and its cache / state
+    auto build_mixer = [&](LayeredLayerW& lw, int i, int base) {
         const fl_layer_desc& d = lw.d;
-        check_layer(m, i, d);
         const size_t H = d.heads, D = d.dim, Dv = d.vdim;
-        const bool pre = !c.no_pre_norm;
-        if (pre) reg(&lw.norm1, W * 4);
-        reg(&lw.norm1b, W * 4);
-        auto pad8 = [](int n) { return (n + 7) / 8 * 8; };
-        auto recurrent = [&](size_t rows) {            // a per-slot state [heads][rows][vdim] + the per-head decay parameters
+        auto recurrent = [&]() {                        // a per-slot state [heads][rows][vdim] + the per-head decay parameters
             lw.gla_index = (int)m.gla_layers.size();
-            m.gla_layers.push_back(i);
-            (void)rows;
+            m.gla_layers.push_back(&lw);
             m.max_heads = std::max<int>(m.max_heads, (int)H);
         };
-        if (d.mixer == FL_MIXER_ATTN) {
-            if (lw.d.kv_heads <= 0) lw.d.kv_heads = lw.d.heads;
-            const size_t G = lw.d.kv_heads;
-            lw.off_q = 0; lw.n_in = (int)(H * D); lw.off_k = lw.off_v = -1;
-            reg(&lw.qnorm, D * 4);
-            m.max_av = std::max<int>(m.max_av, (int)Dv);
-            if (d.kv_from < 0) {
-                lw.off_k = lw.n_in; lw.off_v = lw.off_k + (int)(G * D); lw.n_in = lw.off_v + (int)(G * Dv);
-                reg(&lw.knorm, D * 4);
-                lw.kv_owner = i;
-                lw.kv_index = (int)m.kv_layers.size();
-                m.kv_layers.push_back(i);
-            } else {
-                lw.kv_owner = d.kv_from;
-                lw.kv_index = m.layers[d.kv_from].kv_index;
-            }
-            lw.n_in = pad8(lw.n_in);
+        auto rope = [&]() {
             const RopeSpec rs{d.rot_dims, d.rot_base, d.yarn_factor, d.yarn_original, d.yarn_fast, d.yarn_slow};
             int ri = -1;
             for (size_t k = 0; k < m.ropes.size(); ++k)
                 if (m.ropes[k] == rs) ri = (int)k;
             if (ri < 0) { ri = (int)m.ropes.size(); m.ropes.push_back(rs); }
             lw.rope_index = ri;
+        };
+        if (d.mixer == FL_MIXER_ATTN) {
+            if (lw.d.kv_heads <= 0) lw.d.kv_heads = lw.d.heads;
+            const size_t G = lw.d.kv_heads;
+            lw.off_q = 0; lw.n_in = (int)(H * D); lw.off_k = lw.off_v = -1;
+            if (!d.no_qk_norm) reg(&lw.qnorm, D * 4);
+            m.max_av = std::max<int>(m.max_av, (int)Dv);
+            if (d.kv_from < 0) {
+                lw.off_k = lw.n_in; lw.off_v = lw.off_k + (int)(G * D); lw.n_in = lw.off_v + (int)(G * Dv);
+                if (!d.no_qk_norm) reg(&lw.knorm, D * 4);
+                lw.kv_owner = i;
+                lw.kv_index = (int)m.kv_layers.size();
+                m.kv_layers.push_back(&lw);
+            } else {
+                lw.kv_owner = d.kv_from;
+                lw.kv_index = m.layers[d.kv_from].kv_index;
+            }
+            lw.n_in = pad8(lw.n_in);
+            rope();
         } else if (d.mixer == FL_MIXER_MAMBA2) {
             const size_t inner = H * Dv, GN = (size_t)d.groups * d.state;
             lw.off_g = 0;                               // z, the output gate
@@ -165,7 +184,7 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             lw.conv_off = (int)inner; lw.conv_ch = (int)(inner + 2 * GN);
             reg(&lw.conv_w, (size_t)lw.conv_ch * d.conv * 4); reg(&lw.conv_b, (size_t)lw.conv_ch * 4);
             reg(&lw.a_log, H * 4); reg(&lw.dt_bias, H * 4); reg(&lw.dskip, H * 4); reg(&lw.hnorm, inner * 4);
-            recurrent(d.state);
+            recurrent();
         } else if (d.mixer == FL_MIXER_DELTA) {
             if (lw.d.kv_heads <= 0) lw.d.kv_heads = lw.d.heads;
             const size_t G = lw.d.kv_heads;
@@ -175,14 +194,14 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             lw.conv_off = 0; lw.conv_ch = lw.off_g;
             reg(&lw.conv_w, (size_t)lw.conv_ch * d.conv * 4);
             reg(&lw.a_log, H * 4); reg(&lw.dt_bias, H * 4); reg(&lw.hnorm, Dv * 4);
-            recurrent(D);
+            recurrent();
         } else if (d.mixer == FL_MIXER_GLA) {
             lw.off_q = 0; lw.off_k = (int)(H * D); lw.off_v = (int)(2 * H * D); lw.off_g = lw.off_v + (int)(H * Dv);
             lw.off_a = lw.off_g + (int)(H * Dv);
             lw.n_in = lw.off_a + d.decay_rank;
             reg(&lw.a2, H * D * d.decay_rank * 2); reg(&lw.a2b, H * D * 4); reg(&lw.hnorm, Dv * 4);
             lw.gla_index = (int)m.gla_layers.size();
-            m.gla_layers.push_back(i);
+            m.gla_layers.push_back(&lw);
             m.max_hd = std::max<int>(m.max_hd, (int)(H * D));
         } else {
             const size_t R = d.rot_dim, C = d.kv_rank;
@@ -193,35 +212,63 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
                 reg(&lw.dkv_norm, C * 4);
                 lw.kv_owner = i;
                 lw.kv_index = (int)m.kv_layers.size();
-                m.kv_layers.push_back(i);
+                m.kv_layers.push_back(&lw);
             } else {
                 lw.kv_owner = d.kv_from;
                 lw.kv_index = m.layers[d.kv_from].kv_index;
             }
             reg(&lw.uk_t, H * C * D * 2); reg(&lw.uv, H * Dv * C * 2);
-            const RopeSpec rs{d.rot_dims, d.rot_base, d.yarn_factor, d.yarn_original, d.yarn_fast, d.yarn_slow};
-            int ri = -1;
-            for (size_t k = 0; k < m.ropes.size(); ++k)
-                if (m.ropes[k] == rs) ri = (int)k;
-            if (ri < 0) { ri = (int)m.ropes.size(); m.ropes.push_back(rs); }
-            lw.rope_index = ri;
+            rope();
             m.max_hc = std::max<int>(m.max_hc, (int)(H * C));
         }
-        reg(&lw.w_in, (size_t)lw.n_in * W * 2);
+        if (base > 0) {             // rows of a second mixer: shift its offsets behind the first one's
+            for (int* o : {&lw.off_q, &lw.off_k, &lw.off_v, &lw.off_g, &lw.off_a, &lw.off_dkv, &lw.off_b, &lw.off_dt})
+                if (*o >= 0) *o += base;
+            lw.conv_off += base;
+        }
         reg(&lw.w_o, W * H * Dv * 2);
-        m.max_in = std::max(m.max_in, lw.n_in);
         m.max_hv = std::max<int>(m.max_hv, (int)(H * Dv));
         m.max_cv = std::max(m.max_cv, lw.conv_ch);
+    };
+    int next_desc = 0;
+    for (int i = 0; i < m.L; ++i) {
+        LayeredLayerW& lw = m.layers[i];
+        lw.d = descs[next_desc++];
+        const fl_layer_desc& d = lw.d;
+        check_layer(m, i, d);
+        const bool pre = !c.no_pre_norm, post = !c.no_post_norm;
+        if (pre) reg(&lw.norm1, W * 4);
+        if (post) reg(&lw.norm1b, W * 4);
+        build_mixer(lw, i, 0);
+        if (d.beside) {
+            FL_CHECK(!post, FL_ERR_UNSUPPORTED, "mixers side by side are built for stacks whose sublayer results join the stream un-normed");
+            lw.side = std::make_shared<LayeredLayerW>();
+            lw.side->d = descs[next_desc++];
+            lw.side->d.beside = 0;
+            check_mixer(m, i, lw.side->d, true);
+            build_mixer(*lw.side, i, lw.n_in);
+            lw.n_in += lw.side->n_in;
+            lw.side->n_in = lw.n_in;                    // both read rows of the same projected buffer
+            reg(&lw.pair_wa, W * 4); reg(&lw.pair_wb, W * 4);
+        }
+        reg(&lw.w_in, (size_t)lw.n_in * W * 2);
+        m.max_in = std::max(m.max_in, lw.n_in);
+        if (c.canon_taps > 0) { reg(&lw.canon1, W * c.canon_taps * 4); lw.canon_index = i; }
+        if (c.gated_residual) { reg(&lw.rg1, W * W * 2); reg(&lw.rg1b, W * 4); }
+        if (c.depth_avg) reg(&lw.dwa, (size_t)(i + 2) * 4);
         if (d.ffn != FL_FFN_NONE) {
             if (pre) reg(&lw.norm2, W * 4);
-            reg(&lw.norm2b, W * 4);
+            if (post) reg(&lw.norm2b, W * 4);
+            if (c.canon_taps > 0) reg(&lw.canon2, W * c.canon_taps * 4);
+            if (c.gated_residual) { reg(&lw.rg2, W * W * 2); reg(&lw.rg2b, W * 4); }
             if (d.ffn == FL_FFN_DENSE && d.ffn_bias) { reg(&lw.b_gu, (size_t)2 * d.ff * 4); reg(&lw.b_down, W * 4); }
-            const size_t G = d.ffn == FL_FFN_MOE ? d.experts : 1, F = d.ff;
-            reg(&lw.w_gu, G * 2 * F * W * 2); reg(&lw.w_down, G * W * F * 2);
+            const size_t G = d.ffn == FL_FFN_MOE ? d.experts : 1, F = d.ff, GF = d.ffn_act == FL_ACT_RELU2 ? F : 2 * F;
+            reg(&lw.w_gu, G * GF * W * 2); reg(&lw.w_down, G * W * F * 2);
             m.max_ff = std::max<int>(m.max_ff, (int)F);
             m.max_top = std::max(m.max_top, d.ffn == FL_FFN_MOE ? d.top : 1);
             if (d.ffn == FL_FFN_MOE) {
                 reg(&lw.router, (size_t)d.experts * W * 4);
+                if (d.router == FL_ROUTER_SIGMOID_GROUPS) reg(&lw.route_corr, (size_t)d.experts * 4);
                 m.max_experts = std::max(m.max_experts, d.experts);
                 if (d.shared_ff > 0) {
                     reg(&lw.s_gu, (size_t)2 * d.shared_ff * W * 2); reg(&lw.s_down, W * (size_t)d.shared_ff * 2);
@@ -236,7 +283,7 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
     m.slab.alloc(total, /*zero=*/true);
     size_t off = 0;
     for (const Reg& r : regs) { *r.pp = m.slab.p + off; off += up256(r.bytes); }
-    m.weight_bytes = total - up256((size_t)m.V * W * 2);
+    m.weight_bytes = total - up256((size_t)m.V * W * 2) - (c.max_positions > 0 ? up256((size_t)c.max_positions * W * 2) : 0);
 
     // names -> destinations
     LayeredRoutes R;
@@ -245,62 +292,85 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
     };
     auto vec = [&](const std::string& n, float* base, int64_t rows, int64_t cols) { R.r[n] = LyRoute{LyRoute::F32, base, rows, cols, 0}; };
     mat("embed", m.embed, 0, m.V, W); mat("head", m.head, 0, m.V, W); vec("final.norm", m.final_norm, W, 1);
+    if (m.pos != nullptr) mat("pos", m.pos, 0, c.max_positions, W);
+    // the tensors of one mixer, named p + "q" and so on (p = "l<i>.mix." or "l<i>.mix.left." / "l<i>.mix.right.")
+    auto route_mixer = [&](const LayeredLayerW& lw, const std::string& p) {
+        const fl_layer_desc& d = lw.d;
+        const int64_t H = d.heads, D = d.dim, Dv = d.vdim;
+        if (d.mixer == FL_MIXER_ATTN) {
+            const int64_t G = d.kv_heads;
+            mat(p + "q", lw.w_in, lw.off_q, H * D, W);
+            if (!d.no_qk_norm) vec(p + "q.norm", lw.qnorm, D, 1);
+            if (d.kv_from < 0) {
+                mat(p + "k", lw.w_in, lw.off_k, G * D, W); mat(p + "v", lw.w_in, lw.off_v, G * Dv, W);
+                if (!d.no_qk_norm) vec(p + "k.norm", lw.knorm, D, 1);
+            }
+        } else if (d.mixer == FL_MIXER_MAMBA2) {
+            mat(p + "in", lw.w_in, lw.off_g, lw.off_dt - lw.off_g + H, W);
+            vec(p + "conv", lw.conv_w, lw.conv_ch, d.conv); vec(p + "conv.b", lw.conv_b, lw.conv_ch, 1);
+            vec(p + "dt_bias", lw.dt_bias, H, 1); vec(p + "A_log", lw.a_log, H, 1); vec(p + "D", lw.dskip, H, 1);
+            vec(p + "norm", lw.hnorm, H * Dv, 1);
+        } else if (d.mixer == FL_MIXER_DELTA) {
+            const int64_t G = d.kv_heads;
+            mat(p + "q", lw.w_in, lw.off_q, G * D, W); mat(p + "k", lw.w_in, lw.off_k, G * D, W);
+            mat(p + "v", lw.w_in, lw.off_v, H * Dv, W); mat(p + "g", lw.w_in, lw.off_g, H * Dv, W);
+            mat(p + "b", lw.w_in, lw.off_b, H, W); mat(p + "a", lw.w_in, lw.off_a, H, W);
+            vec(p + "q.conv", lw.conv_w + (size_t)(lw.off_q - lw.conv_off) * d.conv, G * D, d.conv);
+            vec(p + "k.conv", lw.conv_w + (size_t)(lw.off_k - lw.conv_off) * d.conv, G * D, d.conv);
+            vec(p + "v.conv", lw.conv_w + (size_t)(lw.off_v - lw.conv_off) * d.conv, H * Dv, d.conv);
+            vec(p + "A_log", lw.a_log, H, 1); vec(p + "dt_bias", lw.dt_bias, H, 1); vec(p + "norm", lw.hnorm, Dv, 1);
+        } else if (d.mixer == FL_MIXER_GLA) {
+            mat(p + "q", lw.w_in, lw.off_q, H * D, W); mat(p + "k", lw.w_in, lw.off_k, H * D, W);
+            mat(p + "v", lw.w_in, lw.off_v, H * Dv, W); mat(p + "g", lw.w_in, lw.off_g, H * Dv, W);
+            mat(p + "a1", lw.w_in, lw.off_a, d.decay_rank, W);
+            mat(p + "a2", lw.a2, 0, H * D, d.decay_rank); vec(p + "a2.b", lw.a2b, H * D, 1); vec(p + "norm", lw.hnorm, Dv, 1);
+        } else {
+            const int64_t Rr = d.rot_dim, C = d.kv_rank;
+            mat(p + "q", lw.w_in, lw.off_q, H * (D + Rr), W);
+            if (d.kv_from < 0) { mat(p + "dkv", lw.w_in, lw.off_dkv, C + Rr, W); vec(p + "dkv.norm", lw.dkv_norm, C, 1); }
+            R.r[p + "uk"] = LyRoute{LyRoute::UK_T, lw.uk_t, H * D, C, (int)H};
+            mat(p + "uv", lw.uv, 0, H * Dv, C);
+        }
+        mat(p + "o", lw.w_o, 0, W, H * Dv);
+    };
     for (int i = 0; i < m.L; ++i) {
         LayeredLayerW& lw = m.layers[i];
         const fl_layer_desc& d = lw.d;
         const std::string p = "l" + std::to_string(i) + ".";
-        const int64_t H = d.heads, D = d.dim, Dv = d.vdim;
-        const bool pre = !c.no_pre_norm;
-        if (pre) { vec(p + "norm1", lw.norm1, W, 1); vec(p + "norm1b", lw.norm1b, W, 1); }
-        else vec(p + "norm1", lw.norm1b, W, 1);
-        if (d.mixer == FL_MIXER_ATTN) {
-            const int64_t G = d.kv_heads;
-            mat(p + "mix.q", lw.w_in, lw.off_q, H * D, W); vec(p + "mix.q.norm", lw.qnorm, D, 1);
-            if (d.kv_from < 0) {
-                mat(p + "mix.k", lw.w_in, lw.off_k, G * D, W); mat(p + "mix.v", lw.w_in, lw.off_v, G * Dv, W);
-                vec(p + "mix.k.norm", lw.knorm, D, 1);
-            }
-        } else if (d.mixer == FL_MIXER_MAMBA2) {
-            mat(p + "mix.in", lw.w_in, 0, lw.off_dt + H, W);
-            vec(p + "mix.conv", lw.conv_w, lw.conv_ch, d.conv); vec(p + "mix.conv.b", lw.conv_b, lw.conv_ch, 1);
-            vec(p + "mix.dt_bias", lw.dt_bias, H, 1); vec(p + "mix.A_log", lw.a_log, H, 1); vec(p + "mix.D", lw.dskip, H, 1);
-            vec(p + "mix.norm", lw.hnorm, H * Dv, 1);
-        } else if (d.mixer == FL_MIXER_DELTA) {
-            const int64_t G = d.kv_heads;
-            mat(p + "mix.q", lw.w_in, lw.off_q, G * D, W); mat(p + "mix.k", lw.w_in, lw.off_k, G * D, W);
-            mat(p + "mix.v", lw.w_in, lw.off_v, H * Dv, W); mat(p + "mix.g", lw.w_in, lw.off_g, H * Dv, W);
-            mat(p + "mix.b", lw.w_in, lw.off_b, H, W); mat(p + "mix.a", lw.w_in, lw.off_a, H, W);
-            vec(p + "mix.q.conv", lw.conv_w + (size_t)lw.off_q * d.conv, G * D, d.conv);
-            vec(p + "mix.k.conv", lw.conv_w + (size_t)lw.off_k * d.conv, G * D, d.conv);
-            vec(p + "mix.v.conv", lw.conv_w + (size_t)lw.off_v * d.conv, H * Dv, d.conv);
-            vec(p + "mix.A_log", lw.a_log, H, 1); vec(p + "mix.dt_bias", lw.dt_bias, H, 1); vec(p + "mix.norm", lw.hnorm, Dv, 1);
-        } else if (d.mixer == FL_MIXER_GLA) {
-            mat(p + "mix.q", lw.w_in, lw.off_q, H * D, W); mat(p + "mix.k", lw.w_in, lw.off_k, H * D, W);
-            mat(p + "mix.v", lw.w_in, lw.off_v, H * Dv, W); mat(p + "mix.g", lw.w_in, lw.off_g, H * Dv, W);
-            mat(p + "mix.a1", lw.w_in, lw.off_a, d.decay_rank, W);
-            mat(p + "mix.a2", lw.a2, 0, H * D, d.decay_rank); vec(p + "mix.a2.b", lw.a2b, H * D, 1); vec(p + "mix.norm", lw.hnorm, Dv, 1);
+        const bool pre = !c.no_pre_norm, post = !c.no_post_norm;
+        if (pre && post) { vec(p + "norm1", lw.norm1, W, 1); vec(p + "norm1b", lw.norm1b, W, 1); }
+        else vec(p + "norm1", pre ? lw.norm1 : lw.norm1b, W, 1);
+        if (lw.side) {
+            lw.side->w_in = lw.w_in;
+            route_mixer(lw, p + "mix.left."); route_mixer(*lw.side, p + "mix.right.");
+            vec(p + "mix.left.out", lw.pair_wa, W, 1); vec(p + "mix.right.out", lw.pair_wb, W, 1);
         } else {
-            const int64_t Rr = d.rot_dim, C = d.kv_rank;
-            mat(p + "mix.q", lw.w_in, 0, H * (D + Rr), W);
-            if (d.kv_from < 0) { mat(p + "mix.dkv", lw.w_in, lw.off_dkv, C + Rr, W); vec(p + "mix.dkv.norm", lw.dkv_norm, C, 1); }
-            R.r[p + "mix.uk"] = LyRoute{LyRoute::UK_T, lw.uk_t, H * D, C, (int)H};
-            mat(p + "mix.uv", lw.uv, 0, H * Dv, C);
+            route_mixer(lw, p + "mix.");
         }
-        mat(p + "mix.o", lw.w_o, 0, W, H * Dv);
+        if (lw.canon1) vec(p + "canon1", lw.canon1, W, c.canon_taps);
+        if (lw.rg1) { mat(p + "rg1", lw.rg1, 0, W, W); vec(p + "rg1.b", lw.rg1b, W, 1); }
+        if (lw.dwa) vec(p + "dwa", lw.dwa, i + 2, 1);
         if (d.ffn == FL_FFN_NONE) continue;
-        if (pre) { vec(p + "norm2", lw.norm2, W, 1); vec(p + "norm2b", lw.norm2b, W, 1); }
-        else vec(p + "norm2", lw.norm2b, W, 1);
+        if (pre && post) { vec(p + "norm2", lw.norm2, W, 1); vec(p + "norm2b", lw.norm2b, W, 1); }
+        else vec(p + "norm2", pre ? lw.norm2 : lw.norm2b, W, 1);
+        if (lw.canon2) vec(p + "canon2", lw.canon2, W, c.canon_taps);
+        if (lw.rg2) { mat(p + "rg2", lw.rg2, 0, W, W); vec(p + "rg2.b", lw.rg2b, W, 1); }
         const int64_t F = d.ff;
+        const bool gated = d.ffn_act != FL_ACT_RELU2;
+        const int64_t GF = gated ? 2 * F : F;
         if (d.ffn == FL_FFN_DENSE) {
-            mat(p + "mlp.gate", lw.w_gu, 0, F, W); mat(p + "mlp.up", lw.w_gu, F, F, W); mat(p + "mlp.down", lw.w_down, 0, W, F);
+            if (gated) mat(p + "mlp.gate", lw.w_gu, 0, F, W);
+            mat(p + "mlp.up", lw.w_gu, gated ? F : 0, F, W); mat(p + "mlp.down", lw.w_down, 0, W, F);
             if (d.ffn_bias) {
                 vec(p + "mlp.gate.b", lw.b_gu, F, 1); vec(p + "mlp.up.b", lw.b_gu + F, F, 1); vec(p + "mlp.down.b", lw.b_down, W, 1);
             }
         } else {
             vec(p + "mlp.router", lw.router, d.experts, W);
+            if (lw.route_corr) vec(p + "mlp.correction", lw.route_corr, d.experts, 1);
             for (int e = 0; e < d.experts; ++e) {
                 const std::string q = p + "mlp.e" + std::to_string(e) + ".";
-                mat(q + "gate", lw.w_gu, (int64_t)e * 2 * F, F, W); mat(q + "up", lw.w_gu, (int64_t)e * 2 * F + F, F, W);
+                if (gated) mat(q + "gate", lw.w_gu, (int64_t)e * GF, F, W);
+                mat(q + "up", lw.w_gu, (int64_t)e * GF + (gated ? F : 0), F, W);
                 mat(q + "down", lw.w_down, (int64_t)e * W, W, F);
             }
             if (d.shared_ff > 0) {
@@ -363,12 +433,13 @@ void layered_random_init(LayeredModel& m, uint64_t seed, float stdv) {
         if (r->kind == LyRoute::F32) {
             auto ends = [&](const char* t) { const size_t k = std::strlen(t); return n.size() >= k && n.compare(n.size() - k, k, t) == 0; };
             // a plain norm weight sits around one, a zero-centred one around zero
-            const bool around_one = ends("mix.norm") || ends("dkv.norm") || ends("q.norm") || ends("k.norm") || ends("mix.D") ||
+            const bool around_one = ends("mix.norm") || ends("dkv.norm") || ends("q.norm") || ends("k.norm") || ends("mix.D") || ends("left.out") || ends("right.out") ||
                                     (m.cfg.norm_plain && (ends("norm1") || ends("norm2") || ends("norm1b") || ends("norm2b") || n == "final.norm"));
             const bool is_mat = n.find("router") != std::string::npos || n.find("mix.a2") != std::string::npos || n.find("shared.sg") != std::string::npos ||
-                                ends(".conv");
+                                ends(".conv") || ends(".canon1") || ends(".canon2");
             const bool is_bias = n.size() >= 4 && n.compare(n.size() - 4, 4, "a2.b") == 0;
             if (around_one) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 1.0f);
+            else if (ends(".dwa")) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 1.0f / (float)numel);     // a plain mean over the outputs so far
             else if (is_bias) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 3.0f);
             else if (is_mat) synth_fill_f32_kernel<<<kNumSMs, 256>>>((float*)r->dst, numel, ts, stdv, ident);
             else fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 0.0f);
@@ -401,16 +472,19 @@ void layered_finalize(LayeredModel& m) {
             const fl_layer_desc& d = lw.d;
             map(lw.w_in, lw.n_in, m.W, lw.tm_in, lw.tc_in);
             map(lw.w_o, m.W, d.heads * d.vdim, lw.tm_o, lw.tc_o);
-            if (d.ffn == FL_FFN_DENSE) { map(lw.w_gu, 2 * d.ff, m.W, lw.tm_gu, lw.tc_gu); map(lw.w_down, m.W, d.ff, lw.tm_down, lw.tc_down); }
+            if (lw.side) map(lw.side->w_o, m.W, lw.side->d.heads * lw.side->d.vdim, lw.side->tm_o, lw.side->tc_o);
+            map(lw.rg1, m.W, m.W, lw.tm_rg1, lw.tc_rg1); map(lw.rg2, m.W, m.W, lw.tm_rg2, lw.tc_rg2);
+            const int GF = d.ffn_act == FL_ACT_RELU2 ? d.ff : 2 * d.ff;       // rows of the first feed-forward matrix: up, or gate | up
+            if (d.ffn == FL_FFN_DENSE) { map(lw.w_gu, GF, m.W, lw.tm_gu, lw.tc_gu); map(lw.w_down, m.W, d.ff, lw.tm_down, lw.tc_down); }
             if (d.ffn == FL_FFN_MOE && d.shared_ff > 0) {
                 map(lw.s_gu, 2 * d.shared_ff, m.W, lw.tm_sgu, lw.tc_sgu); map(lw.s_down, m.W, d.shared_ff, lw.tm_sdown, lw.tc_sdown);
             }
-            if (d.ffn == FL_FFN_MOE && fits(2 * d.ff, m.W) && fits(m.W, d.ff)) {
+            if (d.ffn == FL_FFN_MOE && fits(GF, m.W) && fits(m.W, d.ff)) {
                 lw.tc_moe = true;
-                lw.tm_gu = make_tmap_bf16(lw.w_gu, (uint64_t)d.experts * 2 * d.ff, (uint64_t)m.W, (uint64_t)m.W, 128);
+                lw.tm_gu = make_tmap_bf16(lw.w_gu, (uint64_t)d.experts * GF, (uint64_t)m.W, (uint64_t)m.W, 128);
                 lw.tm_down = make_tmap_bf16(lw.w_down, (uint64_t)d.experts * m.W, (uint64_t)d.ff, (uint64_t)d.ff, 128);
                 for (int e = 0; e < d.experts; ++e) {
-                    lw.tm_egu.push_back(make_tmap_bf16(lw.w_gu + (size_t)e * 2 * d.ff * m.W, 2 * (uint64_t)d.ff, (uint64_t)m.W, (uint64_t)m.W, 128));
+                    lw.tm_egu.push_back(make_tmap_bf16(lw.w_gu + (size_t)e * GF * m.W, (uint64_t)GF, (uint64_t)m.W, (uint64_t)m.W, 128));
                     lw.tm_edown.push_back(make_tmap_bf16(lw.w_down + (size_t)e * m.W * d.ff, (uint64_t)m.W, (uint64_t)d.ff, (uint64_t)d.ff, 128));
                 }
             }
@@ -461,7 +535,7 @@ void layered_cache_create(fl_cache& c, int max_slots, int max_seq, int pool_toke
     const size_t esz = m.f32 ? 4 : 2;
     y.kv_store.resize(m.kv_layers.size());
     for (size_t k = 0; k < m.kv_layers.size(); ++k) {
-        const fl_layer_desc& d = m.layers[m.kv_layers[k]].d;
+        const fl_layer_desc& d = m.kv_layers[k]->d;
         const size_t width = d.mixer == FL_MIXER_ATTN ? (size_t)d.kv_heads * (d.dim + d.vdim) : (size_t)(d.kv_rank + d.rot_dim);
         y.kv_store[k].alloc((size_t)pages * kKvPage * width * esz, true);
         y.kv_pool.push_back(y.kv_store[k].p);
@@ -469,11 +543,15 @@ void layered_cache_create(fl_cache& c, int max_slots, int max_seq, int pool_toke
     y.gla_state.resize(m.gla_layers.size());
     y.conv_state.resize(m.gla_layers.size());
     for (size_t k = 0; k < m.gla_layers.size(); ++k) {
-        const LayeredLayerW& lw = m.layers[m.gla_layers[k]];
+        const LayeredLayerW& lw = *m.gla_layers[k];
         const fl_layer_desc& d = lw.d;
         const size_t rows = d.mixer == FL_MIXER_MAMBA2 ? d.state : d.dim;
         y.gla_state[k].alloc((size_t)max_slots * d.heads * rows * d.vdim, true);
         if (lw.conv_ch > 0 && d.conv > 1) y.conv_state[k].alloc((size_t)max_slots * (d.conv - 1) * lw.conv_ch, true);
+    }
+    if (m.cfg.canon_taps > 1) {
+        y.canon_state.resize(m.L);
+        for (int i = 0; i < m.L; ++i) y.canon_state[i].alloc((size_t)2 * max_slots * (m.cfg.canon_taps - 1) * m.W, true);
     }
     y.rope_cos.resize(m.ropes.size()); y.rope_sin.resize(m.ropes.size());
     for (size_t k = 0; k < m.ropes.size(); ++k) {
@@ -518,6 +596,11 @@ static void ensure_ws(fl_cache& c, size_t T, size_t n_want) {
         y.proj.alloc(R * m.max_in); y.u.alloc(R * std::max(m.max_hv, 1)); y.go.alloc(R * std::max(m.max_hv, 1));
         y.la.alloc(R * std::max(m.max_hd, 1));
         y.cv.alloc(R * std::max(m.max_cv, 1)); y.rs.alloc(R * 2 * std::max(m.max_heads, 1));
+        if (m.cfg.canon_taps > 0) y.hc.alloc(R * W);
+        if (m.cfg.gated_residual) y.gz.alloc(R * W);
+        if (m.cfg.depth_avg) y.xs.alloc((size_t)(m.L + 1) * R * W);
+        for (const LayeredLayerW& lw : m.layers)
+            if (lw.side && y.y2.n < R * W) y.y2.alloc(R * W);
         y.qa.alloc(R * std::max(m.max_hc, 1)); y.ol.alloc(R * std::max(m.max_hc, 1));
         y.gu.alloc(P * 2 * std::max(m.max_ff, 1)); y.act.alloc(P * std::max(m.max_ff, 1)); y.eo.alloc(P * W);
         y.sh_gu.alloc(R * 2 * std::max(m.max_ff, 1)); y.sh_act.alloc(R * std::max(m.max_ff, 1)); y.sh_o.alloc(R * W);
@@ -533,11 +616,11 @@ static void ensure_ws(fl_cache& c, size_t T, size_t n_want) {
             size_t gx_rows = 0;
             for (const LayeredLayerW& lw : m.layers) {          // grouped expert GEMMs: [slices][experts * cap rows][2 ff | W]
                 if (!lw.tc_moe) continue;
-                const int E = lw.d.experts, F = lw.d.ff;
+                const int E = lw.d.experts, F = lw.d.ff, GF = lw.d.ffn_act == FL_ACT_RELU2 ? F : 2 * F;
                 gx_rows = std::max<size_t>(gx_rows, (size_t)E * 128);
                 for (int cap = 16; cap <= 128; cap *= 2) {
-                    const int k1 = pick_ksplit(E * ((2 * F + 127) / 128), (int)(W + 63) / 64, cap), k2 = pick_ksplit(E * ((int)(W + 127) / 128), (F + 63) / 64, cap);
-                    need = std::max(need, std::max((size_t)k1 * E * cap * 2 * F, (size_t)k2 * E * cap * W));
+                    const int k1 = pick_ksplit(E * ((GF + 127) / 128), (int)(W + 63) / 64, cap), k2 = pick_ksplit(E * ((int)(W + 127) / 128), (F + 63) / 64, cap);
+                    need = std::max(need, std::max((size_t)k1 * E * cap * GF, (size_t)k2 * E * cap * W));
                 }
             }
             if (y.gemm_out.n < need) y.gemm_out.alloc(need);
@@ -782,6 +865,7 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
         seen[sl] = 1;
         FL_CHECK(counts[i] >= 1, FL_ERR_INVALID, "every sequence of a step brings at least one token");
         FL_CHECK(c.slot_len[sl] + counts[i] <= c.max_seq, FL_ERR_STATE, "sequence longer than the cache's max_seq");
+        FL_CHECK(m.cfg.max_positions <= 0 || c.slot_len[sl] + counts[i] <= m.cfg.max_positions, FL_ERR_STATE, "sequence longer than the model's position table");
         need_pages += y.pool.missing(sl, c.slot_len[sl] + counts[i]);
         T += counts[i];
     }
@@ -862,6 +946,130 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
     for (int i = 0; i < n; ++i) c.slot_len[slots[i]] += counts[i];
 }
 
+// One mixer over all rows of the step: reads its columns of the projected buffer y.proj (row stride lw.n_in), its cache pages / state
+// slots, and leaves the mixer's inner output (what its output projection reads) in y.u with the hi | lo halves when that
+// projection runs on the tensor cores.
+static void run_mixer(fl_cache& c, LaunchCtx& lc, const StepTab& st, const LayeredLayerW& lw, const int* slots, const int* counts, int n,
+                      const int* h_row0, const int* h_pos0) {
+    const LayeredModel& m = *c.lm;
+    LayeredCache& y = *c.ly;
+    const fl_layer_desc& d = lw.d;
+    const int Ti = st.T, H = d.heads, D = d.dim, Dv = d.vdim;
+    const float eps = m.cfg.norm_eps;
+    uint16_t *uhi = m.f32 ? nullptr : y.u_hi.p, *ulo = m.f32 ? nullptr : y.u_lo.p;
+    if (d.mixer == FL_MIXER_ATTN) {
+        const int G = d.kv_heads;
+        AttnPrepArgs pa{y.proj.p, lw.n_in, lw.off_q, lw.off_k, lw.off_v, lw.qnorm, lw.knorm, eps, y.kv_pool[lw.kv_index], y.page_table.p,
+                        c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot, y.rope_cos[lw.rope_index].p, y.rope_sin[lw.rope_index].p,
+                        H, G, D, Dv, d.rot_dims, d.rot_halves};
+        const size_t psm = (size_t)4 * D * 4;
+        if (m.f32) launch(lc, "attn_prep", 0, ly_attn_prep_kernel<float>, dim3(Ti), dim3(128), psm, pa);
+        else launch(lc, "attn_prep", 0, ly_attn_prep_kernel<uint16_t>, dim3(Ti), dim3(128), psm, pa);
+        GqaAttnArgs at{y.proj.p, lw.n_in, lw.off_q, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot,
+                       y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo, H, G, D, Dv, d.window, d.scale, d.softcap, d.sink, 0, y.at_part.p};
+        // a step of single tokens is replayed from a captured graph whatever the contexts' lengths: its split count must not follow them
+        int max_keys = c.max_seq;
+        if (Ti != n) {
+            max_keys = 1;
+            for (int si = 0; si < n; ++si) max_keys = std::max(max_keys, h_pos0[si] + counts[si]);
+        }
+        if (d.window > 0) max_keys = std::min(max_keys, d.window);
+        // long portions (serving precision): scores and weighted sums as tensor-core GEMMs; decoded tokens, short portions and
+        // the exact mode on the per-(row, head) kernel.  Rows are taken in order.
+        static const bool tc_attn_off = env_flag("FL_LAYERED_NO_TC_ATTN");
+        int done = 0;
+        for (int si = 0; si < n; ++si) {
+            const int r0 = h_row0[si], Ts = counts[si];
+            if (m.f32 || tc_attn_off || Dv % 8 != 0 || Ts < 64 || (long long)Ts * (H / G) <= 128) continue;
+            if (r0 > done) {
+                at.row_base = done;
+                launch_gqa_attn<uint16_t>(lc, at, r0 - done, max_keys, true);
+            }
+            gqa_attn_tc(c, lc, at, r0, Ts, h_pos0[si], slots[si]);
+            done = r0 + Ts;
+        }
+        if (done < Ti) {
+            at.row_base = done;
+            if (m.f32) launch_gqa_attn<float>(lc, at, Ti - done, max_keys, false); else launch_gqa_attn<uint16_t>(lc, at, Ti - done, max_keys, true);
+        }
+    } else if (d.mixer == FL_MIXER_MAMBA2 || d.mixer == FL_MIXER_DELTA) {
+        const bool delta = d.mixer == FL_MIXER_DELTA;
+        const int G = delta ? d.kv_heads : d.groups, rows = delta ? D : d.state;
+        float* cstate = d.conv > 1 ? y.conv_state[lw.gla_index].p : nullptr;
+        ConvArgs ca{y.proj.p, lw.n_in, lw.conv_off, lw.conv_w, lw.conv_b, cstate, st.row_seq, st.row_pos, st.seq_row0, st.seq_slot, st.seq_pos0,
+                    lw.conv_ch, d.conv, y.cv.p};
+        // channel chunks per row: whole q / k heads for the delta rule (they are normalised inside one block)
+        const int chunk = delta ? D * std::max(1, 512 / D) : 512, nchunk = (lw.conv_ch + chunk - 1) / chunk;
+        if (delta)
+            launch(lc, "delta_prep", 0, ly_delta_prep_kernel, dim3(Ti, nchunk), dim3(256), 0, ca, chunk, lw.off_b, lw.off_a, (const float*)lw.dt_bias,
+                   (const float*)lw.a_log, H, G, D, (float)(1.0 / std::sqrt((double)D)), y.rs.p);
+        else
+            launch(lc, "ssm_prep", 0, ly_mamba_prep_kernel, dim3(Ti, nchunk), dim3(256), 0, ca, chunk, lw.off_dt, (const float*)lw.dt_bias,
+                   (const float*)lw.a_log, H, y.rs.p);
+        if (d.conv > 1) launch(lc, "conv_state", 0, ly_conv_state_kernel, dim3(n, (lw.conv_ch + 127) / 128), dim3(128), 0, ca);
+        // column offsets inside cv (the convolved span starts at conv_off)
+        RecArgs ra{y.cv.p, lw.conv_ch, lw.off_q - lw.conv_off, lw.off_k - lw.conv_off, lw.off_v - lw.conv_off, y.rs.p,
+                   delta ? (const float*)nullptr : (const float*)lw.dskip, y.go.p, y.gla_state[lw.gla_index].p, st.seq_row0, st.seq_slot, st.seq_pos0,
+                   H, G, rows, Dv};
+        if (delta) {
+            launch_rec_scan<true>(lc, ra, n);
+            launch(lc, "gla_out", 0, ly_gla_out_kernel, dim3((Ti * H + 7) / 8), dim3(256), 0, (const float*)y.go.p, (const float*)y.proj.p, lw.n_in, lw.off_g,
+                   (const float*)lw.hnorm, eps, Ti, H, Dv, y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
+        } else {
+            launch_rec_scan<false>(lc, ra, n);
+            const int inner = H * Dv, part = inner / d.norm_groups;
+            launch(lc, "gated_group_norm", 0, ly_gated_group_norm_kernel, dim3(Ti, d.norm_groups), dim3(std::min(1024, std::max(64, (part + 31) / 32 * 32))), 0,
+                   (const float*)y.go.p, (const float*)y.proj.p, lw.n_in, lw.off_g, (const float*)lw.hnorm, eps, inner, d.norm_groups, y.u.p,
+                   lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
+        }
+    } else if (d.mixer == FL_MIXER_GLA) {
+        // decay pre-activation through the rank-r bottleneck: z = W_a2 a (the bias and the sigmoid^(1/tau) are applied by the scan)
+        gemm(lc, "gemm_gla_decay", y.proj.p + lw.off_a, lw.n_in, lw.a2, H * D, d.decay_rank, y.la.p, H * D, Ti);
+        GlaArgs ga{y.proj.p, lw.n_in, lw.off_q, lw.off_k, lw.off_v, y.la.p, lw.a2b, 1.f / d.tau, y.go.p, y.gla_state[lw.gla_index].p, st.seq_row0,
+                   st.seq_slot, st.seq_pos0, H, D, Dv, (float)(1.0 / std::sqrt((double)D))};
+        launch_gla_scan(lc, ga, n);
+        launch(lc, "gla_out", 0, ly_gla_out_kernel, dim3((Ti * H + 7) / 8), dim3(256), 0, (const float*)ga.o, (const float*)y.proj.p, lw.n_in, lw.off_g,
+               (const float*)lw.hnorm, eps, Ti, H, Dv, y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
+    } else {
+        const int R = d.rot_dim, C = d.kv_rank;
+        LatentAppendArgs aa{y.proj.p, lw.n_in, lw.off_q, lw.off_dkv, lw.dkv_norm, eps, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq,
+                            st.row_seq, st.row_pos, st.seq_slot, y.rope_cos[lw.rope_index].p, y.rope_sin[lw.rope_index].p, H, D, R, C, d.rot_dims};
+        if (m.f32) launch(lc, "latent_append", 0, ly_latent_append_kernel<float>, dim3(Ti), dim3(128), 0, aa);
+        else launch(lc, "latent_append", 0, ly_latent_append_kernel<uint16_t>, dim3(Ti), dim3(128), 0, aa);
+        // q~[row, h, :] = W_uk[h]^T q_plain[row, h, :]: the score against the latent needs no per-head keys
+        LyGemm qa{y.proj.p + lw.off_q, D + R, lw.n_in, nullptr, lw.uk_t, (long long)C * D, C, D, y.qa.p, C, H * C, nullptr, Ti};
+        gemm_groups(lc, "gemm_q_absorb", qa, H, Ti);
+        LatentAttnArgs at{y.qa.p, y.proj.p, lw.n_in, lw.off_q, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq, st.row_seq, st.row_pos,
+                          st.seq_slot, y.ol.p, H, D, R, C, d.window, d.scale, 0};
+        // long portions (serving precision): scores and weighted sums as tensor-core GEMMs over the gathered window; everything
+        // else (decoded tokens, short portions, the exact mode) on the per-(row, head) kernel.  Rows are taken in order.
+        static const bool tc_attn_off = env_flag("FL_LAYERED_NO_TC_ATTN");
+        int done = 0;           // rows [0, done) are finished
+        for (int si = 0; si < n; ++si) {
+            const int r0 = h_row0[si], Ts = counts[si];
+            if (m.f32 || tc_attn_off || C % 8 != 0 || Ts < 64 || (long long)Ts * H <= 128) continue;
+            if (r0 > done) {
+                at.row_base = done;
+                launch_latent_attn<uint16_t>(lc, at, r0 - done);
+            }
+            latent_attn_tc(c, lc, lw, at, r0, Ts, h_pos0[si], slots[si]);
+            done = r0 + Ts;
+        }
+        if (done < Ti) {
+            at.row_base = done;
+            if (m.f32) launch_latent_attn<float>(lc, at, Ti - done); else launch_latent_attn<uint16_t>(lc, at, Ti - done);
+        }
+        // value expansion after the softmax: out[row, h, :] = W_uv[h] (sum_j p_j c_j)
+        LyGemm ov{y.ol.p, C, H * C, nullptr, lw.uv, (long long)Dv * C, Dv, C, y.u.p, Dv, H * Dv, nullptr, Ti};
+        gemm_groups(lc, "gemm_v_expand", ov, H, Ti);
+        if (lw.tc_o) {
+            const size_t nu = (size_t)Ti * H * Dv;
+            launch(lc, "split_hi_lo", 0, ly_split_kernel, dim3((unsigned)std::min<size_t>(4 * kNumSMs, (nu + 255) / 256)), dim3(256), 0,
+                   (const float*)y.u.p, nu, uhi, ulo);
+        }
+    }
+}
+
 // The device part of a step: every layer over all rows, then the vocabulary projection of the wanted rows.
 static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const int* slots, const int* counts, int n, const int* h_row0,
                          const int* h_pos0) {
@@ -874,143 +1082,71 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
     uint16_t *hhi = m.f32 ? nullptr : y.h_hi.p, *hlo = m.f32 ? nullptr : y.h_lo.p, *uhi = m.f32 ? nullptr : y.u_hi.p, *ulo = m.f32 ? nullptr : y.u_lo.p,
              *ahi = m.f32 ? nullptr : y.act_hi.p, *alo = m.f32 ? nullptr : y.act_lo.p;
     // pre-norm stacks: a sublayer reads h = norm(x) (written by the kernel that last touched x); otherwise it reads x itself and
-    // the same kernel writes x's hi | lo halves for the tensor-core GEMMs
-    const bool pre = !m.cfg.no_pre_norm;
+    // the same kernel writes x's hi | lo halves for the tensor-core GEMMs.  With an input convolution the sublayer reads
+    // hc = h + conv(h) instead (the convolution kernel rewrites the hi | lo halves after the gate's GEMM has read those of h).
+    const bool pre = !m.cfg.no_pre_norm, post = !m.cfg.no_post_norm, canon = m.cfg.canon_taps > 0, gated = m.cfg.gated_residual != 0,
+               depth = m.cfg.depth_avg != 0;
     const int plain = m.cfg.norm_plain ? 1 : 0, split_x = pre ? 0 : 1;
-    const float* sub_in = pre ? y.h.p : y.x.p;
+    const float* norm_out = pre ? y.h.p : y.x.p;                // what the arrangement hands to a sublayer
+    const float* sub_in = canon ? y.hc.p : norm_out;            // what the sublayer's own matrices read
+    const size_t hist_stride = y.rows * (size_t)W;
     launch(lc, "embed_norm", 0, ly_embed_norm_kernel, dim3(Ti), dim3(nthr), 0, (const uint16_t*)m.embed, st.tok, W,
-           pre ? (const float*)m.layers[0].norm1 : (const float*)nullptr, eps, plain, y.x.p, y.h.p, hhi, hlo);
+           pre ? (const float*)m.layers[0].norm1 : (const float*)nullptr, eps, plain, (const uint16_t*)m.pos, st.row_pos, y.x.p,
+           depth ? y.xs.p : (float*)nullptr, y.h.p, hhi, hlo);
+    // in front of a sublayer: the gate's pre-activation from the normed input, then the input convolution (and its carried inputs)
+    auto sublayer_front = [&](const LayeredLayerW& lw, int sub) {
+        if (gated) {
+            const uint16_t* rg = sub == 0 ? lw.rg1 : lw.rg2;
+            gemm_tc_or_exact(c, lc, "gemm_gate", norm_out, hhi, hlo, rg, sub == 0 ? lw.tm_rg1 : lw.tm_rg2, sub == 0 ? lw.tc_rg1 : lw.tc_rg2, W, W, y.gz.p, Ti);
+        }
+        if (canon) {
+            const int taps = m.cfg.canon_taps;
+            float* cs = taps > 1 ? y.canon_state[lw.canon_index].p + (size_t)sub * c.max_batch * (taps - 1) * W : nullptr;
+            ConvArgs ca{norm_out, W, 0, sub == 0 ? lw.canon1 : lw.canon2, nullptr, cs, st.row_seq, st.row_pos, st.seq_row0, st.seq_slot, st.seq_pos0, W, taps, nullptr};
+            launch(lc, "input_conv", 0, ly_input_conv_kernel, dim3(Ti, (W + 255) / 256), dim3(256), 0, ca, y.hc.p, hhi, hlo);
+            if (taps > 1) launch(lc, "conv_state", 0, ly_conv_state_kernel, dim3(n, (W + 127) / 128), dim3(128), 0, ca);
+        }
+    };
     for (int li = 0; li < m.L; ++li) {
         const LayeredLayerW& lw = m.layers[li];
         const fl_layer_desc& d = lw.d;
-        const int H = d.heads, D = d.dim, Dv = d.vdim;
+        const int H = d.heads, Dv = d.vdim;
+        sublayer_front(lw, 0);
         gemm_tc_or_exact(c, lc, "gemm_mix_in", sub_in, hhi, hlo, lw.w_in, lw.tm_in, lw.tc_in, lw.n_in, W, y.proj.p, Ti);
-        if (d.mixer == FL_MIXER_ATTN) {
-            const int G = d.kv_heads;
-            AttnPrepArgs pa{y.proj.p, lw.n_in, lw.off_q, lw.off_k, lw.off_v, lw.qnorm, lw.knorm, eps, y.kv_pool[lw.kv_index], y.page_table.p,
-                            c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot, y.rope_cos[lw.rope_index].p, y.rope_sin[lw.rope_index].p,
-                            H, G, D, Dv, d.rot_dims, d.rot_halves};
-            const size_t psm = (size_t)4 * D * 4;
-            if (m.f32) launch(lc, "attn_prep", 0, ly_attn_prep_kernel<float>, dim3(Ti), dim3(128), psm, pa);
-            else launch(lc, "attn_prep", 0, ly_attn_prep_kernel<uint16_t>, dim3(Ti), dim3(128), psm, pa);
-            GqaAttnArgs at{y.proj.p, lw.n_in, lw.off_q, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot,
-                           y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo, H, G, D, Dv, d.window, d.scale, d.softcap, d.sink, 0, y.at_part.p};
-            // a step of single tokens is replayed from a captured graph whatever the contexts' lengths: its split count must not follow them
-            int max_keys = c.max_seq;
-            if (Ti != n) {
-                max_keys = 1;
-                for (int si = 0; si < n; ++si) max_keys = std::max(max_keys, h_pos0[si] + counts[si]);
-            }
-            // long portions (serving precision): scores and weighted sums as tensor-core GEMMs; decoded tokens, short portions and
-            // the exact mode on the per-(row, head) kernel.  Rows are taken in order.
-            static const bool tc_attn_off = env_flag("FL_LAYERED_NO_TC_ATTN");
-            int done = 0;
-            for (int si = 0; si < n; ++si) {
-                const int r0 = h_row0[si], Ts = counts[si];
-                if (m.f32 || tc_attn_off || Dv % 8 != 0 || Ts < 64 || (long long)Ts * (H / G) <= 128) continue;
-                if (r0 > done) {
-                    at.row_base = done;
-                    launch_gqa_attn<uint16_t>(lc, at, r0 - done, max_keys, true);
-                }
-                gqa_attn_tc(c, lc, at, r0, Ts, h_pos0[si], slots[si]);
-                done = r0 + Ts;
-            }
-            if (done < Ti) {
-                at.row_base = done;
-                if (m.f32) launch_gqa_attn<float>(lc, at, Ti - done, max_keys, false); else launch_gqa_attn<uint16_t>(lc, at, Ti - done, max_keys, true);
-            }
-        } else if (d.mixer == FL_MIXER_MAMBA2 || d.mixer == FL_MIXER_DELTA) {
-            const bool delta = d.mixer == FL_MIXER_DELTA;
-            const int G = delta ? d.kv_heads : d.groups, rows = delta ? D : d.state;
-            float* cstate = d.conv > 1 ? y.conv_state[lw.gla_index].p : nullptr;
-            ConvArgs ca{y.proj.p, lw.n_in, lw.conv_off, lw.conv_w, lw.conv_b, cstate, st.row_seq, st.row_pos, st.seq_row0, st.seq_slot, st.seq_pos0,
-                        lw.conv_ch, d.conv, y.cv.p};
-            // channel chunks per row: whole q / k heads for the delta rule (they are normalised inside one block)
-            const int chunk = delta ? D * std::max(1, 512 / D) : 512, nchunk = (lw.conv_ch + chunk - 1) / chunk;
-            if (delta)
-                launch(lc, "delta_prep", 0, ly_delta_prep_kernel, dim3(Ti, nchunk), dim3(256), 0, ca, chunk, lw.off_b, lw.off_a, (const float*)lw.dt_bias,
-                       (const float*)lw.a_log, H, G, D, (float)(1.0 / std::sqrt((double)D)), y.rs.p);
-            else
-                launch(lc, "ssm_prep", 0, ly_mamba_prep_kernel, dim3(Ti, nchunk), dim3(256), 0, ca, chunk, lw.off_dt, (const float*)lw.dt_bias,
-                       (const float*)lw.a_log, H, y.rs.p);
-            if (d.conv > 1) launch(lc, "conv_state", 0, ly_conv_state_kernel, dim3(n, (lw.conv_ch + 127) / 128), dim3(128), 0, ca);
-            // column offsets inside cv (the convolved span starts at conv_off)
-            RecArgs ra{y.cv.p, lw.conv_ch, lw.off_q - lw.conv_off, lw.off_k - lw.conv_off, lw.off_v - lw.conv_off, y.rs.p,
-                       delta ? (const float*)nullptr : (const float*)lw.dskip, y.go.p, y.gla_state[lw.gla_index].p, st.seq_row0, st.seq_slot, st.seq_pos0,
-                       H, G, rows, Dv};
-            if (delta) {
-                launch_rec_scan<true>(lc, ra, n);
-                launch(lc, "gla_out", 0, ly_gla_out_kernel, dim3((Ti * H + 7) / 8), dim3(256), 0, (const float*)y.go.p, (const float*)y.proj.p, lw.n_in, lw.off_g,
-                       (const float*)lw.hnorm, eps, Ti, H, Dv, y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
-            } else {
-                launch_rec_scan<false>(lc, ra, n);
-                const int inner = H * Dv, part = inner / d.norm_groups;
-                launch(lc, "gated_group_norm", 0, ly_gated_group_norm_kernel, dim3(Ti, d.norm_groups), dim3(std::min(1024, std::max(64, (part + 31) / 32 * 32))), 0,
-                       (const float*)y.go.p, (const float*)y.proj.p, lw.n_in, lw.off_g, (const float*)lw.hnorm, eps, inner, d.norm_groups, y.u.p,
-                       lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
-            }
-        } else if (d.mixer == FL_MIXER_GLA) {
-            // decay pre-activation through the rank-r bottleneck: z = W_a2 a (the bias and the sigmoid^(1/tau) are applied by the scan)
-            gemm(lc, "gemm_gla_decay", y.proj.p + lw.off_a, lw.n_in, lw.a2, H * D, d.decay_rank, y.la.p, H * D, Ti);
-            GlaArgs ga{y.proj.p, lw.n_in, lw.off_q, lw.off_k, lw.off_v, y.la.p, lw.a2b, 1.f / d.tau, y.go.p, y.gla_state[lw.gla_index].p, st.seq_row0,
-                       st.seq_slot, st.seq_pos0, H, D, Dv, (float)(1.0 / std::sqrt((double)D))};
-            launch_gla_scan(lc, ga, n);
-            launch(lc, "gla_out", 0, ly_gla_out_kernel, dim3((Ti * H + 7) / 8), dim3(256), 0, (const float*)ga.o, (const float*)y.proj.p, lw.n_in, lw.off_g,
-                   (const float*)lw.hnorm, eps, Ti, H, Dv, y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
-        } else {
-            const int R = d.rot_dim, C = d.kv_rank;
-            LatentAppendArgs aa{y.proj.p, lw.n_in, lw.off_q, lw.off_dkv, lw.dkv_norm, eps, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq,
-                                st.row_seq, st.row_pos, st.seq_slot, y.rope_cos[lw.rope_index].p, y.rope_sin[lw.rope_index].p, H, D, R, C, d.rot_dims};
-            if (m.f32) launch(lc, "latent_append", 0, ly_latent_append_kernel<float>, dim3(Ti), dim3(128), 0, aa);
-            else launch(lc, "latent_append", 0, ly_latent_append_kernel<uint16_t>, dim3(Ti), dim3(128), 0, aa);
-            // q~[row, h, :] = W_uk[h]^T q_plain[row, h, :]: the score against the latent needs no per-head keys
-            LyGemm qa{y.proj.p + lw.off_q, D + R, lw.n_in, nullptr, lw.uk_t, (long long)C * D, C, D, y.qa.p, C, H * C, nullptr, Ti};
-            gemm_groups(lc, "gemm_q_absorb", qa, H, Ti);
-            LatentAttnArgs at{y.qa.p, y.proj.p, lw.n_in, lw.off_q, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq, st.row_seq, st.row_pos,
-                              st.seq_slot, y.ol.p, H, D, R, C, d.window, d.scale, 0};
-            // long portions (serving precision): scores and weighted sums as tensor-core GEMMs over the gathered window; everything
-            // else (decoded tokens, short portions, the exact mode) on the per-(row, head) kernel.  Rows are taken in order.
-            static const bool tc_attn_off = env_flag("FL_LAYERED_NO_TC_ATTN");
-            int done = 0;           // rows [0, done) are finished
-            for (int si = 0; si < n; ++si) {
-                const int r0 = h_row0[si], Ts = counts[si];
-                if (m.f32 || tc_attn_off || C % 8 != 0 || Ts < 64 || (long long)Ts * H <= 128) continue;
-                if (r0 > done) {
-                    at.row_base = done;
-                    launch_latent_attn<uint16_t>(lc, at, r0 - done);
-                }
-                latent_attn_tc(c, lc, lw, at, r0, Ts, h_pos0[si], slots[si]);
-                done = r0 + Ts;
-            }
-            if (done < Ti) {
-                at.row_base = done;
-                if (m.f32) launch_latent_attn<float>(lc, at, Ti - done); else launch_latent_attn<uint16_t>(lc, at, Ti - done);
-            }
-            // value expansion after the softmax: out[row, h, :] = W_uv[h] (sum_j p_j c_j)
-            LyGemm ov{y.ol.p, C, H * C, nullptr, lw.uv, (long long)Dv * C, Dv, C, y.u.p, Dv, H * Dv, nullptr, Ti};
-            gemm_groups(lc, "gemm_v_expand", ov, H, Ti);
-            if (lw.tc_o) {
-                const size_t nu = (size_t)Ti * H * Dv;
-                launch(lc, "split_hi_lo", 0, ly_split_kernel, dim3((unsigned)std::min<size_t>(4 * kNumSMs, (nu + 255) / 256)), dim3(256), 0,
-                       (const float*)y.u.p, nu, uhi, ulo);
-            }
-        }
+        run_mixer(c, lc, st, lw, slots, counts, n, h_row0, h_pos0);
         gemm_tc_or_exact(c, lc, "gemm_mix_out", y.u.p, uhi, ulo, lw.w_o, lw.tm_o, lw.tc_o, W, H * Dv, y.y.p, Ti);
+        if (lw.side) {
+            const LayeredLayerW& sw = *lw.side;
+            run_mixer(c, lc, st, sw, slots, counts, n, h_row0, h_pos0);
+            gemm_tc_or_exact(c, lc, "gemm_mix_out", y.u.p, uhi, ulo, sw.w_o, sw.tm_o, sw.tc_o, W, sw.d.heads * sw.d.vdim, y.y2.p, Ti);
+        }
         const float* next1 = (pre && li + 1 < m.L) ? m.layers[li + 1].norm1 : nullptr;
         const int more = li + 1 < m.L ? split_x : 0;       // whether another sublayer reads x after this layer
-        launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)nullptr, (const float*)lw.norm1b,
-               d.ffn != FL_FFN_NONE ? (const float*)lw.norm2 : next1, eps, W, plain, d.ffn != FL_FFN_NONE ? split_x : more, y.h.p, hhi, hlo);
-        if (d.ffn == FL_FFN_NONE) continue;
-        const int F = d.ff;
+        const bool has_ff = d.ffn != FL_FFN_NONE;
+        if (post)
+            launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)nullptr, (const float*)lw.norm1b,
+                   has_ff ? (const float*)lw.norm2 : next1, eps, W, plain, has_ff ? split_x : more, y.h.p, hhi, hlo);
+        else
+            launch(lc, "join", 0, ly_join_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, lw.side ? (const float*)y.y2.p : (const float*)nullptr,
+                   (const float*)lw.pair_wa, (const float*)lw.pair_wb, gated ? (const float*)y.gz.p : (const float*)nullptr, (const float*)lw.rg1b,
+                   y.xs.p, hist_stride, (depth && !has_ff) ? li + 1 : -1, (const float*)lw.dwa, has_ff ? (const float*)lw.norm2 : next1, eps, W, plain,
+                   y.h.p, hhi, hlo);
+        if (!has_ff) continue;
+        sublayer_front(lw, 1);
+        const int F = d.ff, act = d.ffn_act, GF = act == FL_ACT_RELU2 ? F : 2 * F;
         if (d.ffn == FL_FFN_DENSE) {
-            gemm_tc_or_exact(c, lc, "gemm_ff_in", sub_in, hhi, hlo, lw.w_gu, lw.tm_gu, lw.tc_gu, 2 * F, W, y.gu.p, Ti);
+            gemm_tc_or_exact(c, lc, "gemm_ff_in", sub_in, hhi, hlo, lw.w_gu, lw.tm_gu, lw.tc_gu, GF, W, y.gu.p, Ti);
             launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
-                   d.ffn_act, (const float*)lw.b_gu, (const int*)nullptr, Ti, lw.tc_down ? (float*)nullptr : y.act.p, lw.tc_down ? ahi : (uint16_t*)nullptr, alo);
+                   act, (const float*)lw.b_gu, (const int*)nullptr, Ti, lw.tc_down ? (float*)nullptr : y.act.p, lw.tc_down ? ahi : (uint16_t*)nullptr, alo);
             gemm_tc_or_exact(c, lc, "gemm_ff_out", y.act.p, ahi, alo, lw.w_down, lw.tm_down, lw.tc_down, W, F, y.y.p, Ti);
         } else {
             const int E = d.experts, top = d.top, P = Ti * top;
-            launch(lc, "moe_router", 0, ly_router_kernel, dim3(Ti), dim3(256), (size_t)E * 4, sub_in, W, (const float*)lw.router, E, top,
-                   (const float*)lw.shared_gate, y.route_sel.p, y.route_w.p, y.sgate.p);
+            if (d.router == FL_ROUTER_SIGMOID_GROUPS)
+                launch(lc, "moe_router", 0, ly_router_sigmoid_kernel, dim3(Ti), dim3(256), ((size_t)2 * E + d.route_groups) * 4, sub_in, W, (const float*)lw.router,
+                       E, top, (const float*)lw.route_corr, d.route_groups, d.route_keep, y.route_sel.p, y.route_w.p);
+            else
+                launch(lc, "moe_router", 0, ly_router_kernel, dim3(Ti), dim3(256), (size_t)E * 4, sub_in, W, (const float*)lw.router, E, top,
+                       (const float*)lw.shared_gate, y.route_sel.p, y.route_w.p, y.sgate.p);
             const float* sh = nullptr;
             if (d.shared_ff > 0) {          // the always-on expert first: its split-K scratch is free again before the routed experts run
                 const int Fs = d.shared_ff;
@@ -1024,9 +1160,9 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
             if (lw.tc_moe && Ti > 128) {
                 // many rows: every expert over all rows on the tensor cores, kept where the row picked it (ascending expert order)
                 for (int e = 0; e < E; ++e) {
-                    dense_gemm(c, lc, "gemm_tc_moe_in", Ti, 2 * F, W, lw.tm_egu[e], y.gu.p, hhi, hlo);
+                    dense_gemm(c, lc, "gemm_tc_moe_in", Ti, GF, W, lw.tm_egu[e], y.gu.p, hhi, hlo);
                     launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
-                           0, (const float*)nullptr, (const int*)nullptr, Ti, (float*)nullptr, ahi, alo);
+                           act, (const float*)nullptr, (const int*)nullptr, Ti, (float*)nullptr, ahi, alo);
                     dense_gemm(c, lc, "gemm_tc_moe_out", Ti, W, F, lw.tm_edown[e], y.eo.p, ahi, alo);
                     launch(lc, "moe_accum", 0, ly_moe_accum_kernel, gw, dim3(256), 0, (const float*)y.eo.p, (const int*)y.route_sel.p,
                            (const float*)y.route_w.p, top, e, (const float*)nullptr, e == 0 ? 1 : 0, W, y.y.p);
@@ -1042,20 +1178,20 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
                     const int cap = Ti <= 16 ? 16 : (Ti <= 32 ? 32 : (Ti <= 64 ? 64 : 128));
                     launch(lc, "moe_gather", 0, ly_moe_gather_kernel, dim3(E, std::min(Ti, 16)), dim3(256), 0, (const uint16_t*)hhi, (const uint16_t*)hlo, W,
                            (const int*)y.grp_off.p, (const int*)y.pair_row.p, cap, y.gx_hi.p, y.gx_lo.p, y.grp_cnt.p);
-                    int ks = dense_gemm_grouped(c, lc, "gemm_tc_moe_in", E, cap, 2 * F, W, lw.tm_gu, y.gemm_out.p, y.gx_hi.p, y.gx_lo.p, y.grp_cnt.p);
-                    FL_CHECK((size_t)ks * E * cap * 2 * F <= y.gemm_out.n, FL_ERR_STATE, "internal: grouped GEMM scratch too small");
+                    int ks = dense_gemm_grouped(c, lc, "gemm_tc_moe_in", E, cap, GF, W, lw.tm_gu, y.gemm_out.p, y.gx_hi.p, y.gx_lo.p, y.grp_cnt.p);
+                    FL_CHECK((size_t)ks * E * cap * GF <= y.gemm_out.n, FL_ERR_STATE, "internal: grouped GEMM scratch too small");
                     launch(lc, "glu_grouped", 0, ly_glu_grouped_kernel, dim3((F + 255) / 256, E * cap), dim3(256), 0, (const float*)y.gemm_out.p, ks,
-                           (size_t)E * cap * 2 * F, F, d.limit, (const int*)y.grp_cnt.p, cap, y.ga_hi.p, y.ga_lo.p);
+                           (size_t)E * cap * GF, F, d.limit, act, (const int*)y.grp_cnt.p, cap, y.ga_hi.p, y.ga_lo.p);
                     ks = dense_gemm_grouped(c, lc, "gemm_tc_moe_out", E, cap, W, F, lw.tm_down, y.gemm_out.p, y.ga_hi.p, y.ga_lo.p, y.grp_cnt.p);
                     FL_CHECK((size_t)ks * E * cap * W <= y.gemm_out.n, FL_ERR_STATE, "internal: grouped GEMM scratch too small");
                     launch(lc, "moe_combine", 0, ly_moe_combine_grouped_kernel, gw, dim3(256), 0, (const float*)y.gemm_out.p, ks, (size_t)E * cap * W,
                            (const int*)y.route_sel.p, (const int*)y.pair_of.p, (const int*)y.grp_off.p, cap, (const float*)y.route_w.p, top, sh,
                            (const float*)y.sgate.p, W, y.y.p);
                 } else {
-                    LyGemm g1{sub_in, 0, W, y.pair_row.p, lw.w_gu, (long long)2 * F * W, 2 * F, W, y.gu.p, 0, 2 * F, y.grp_off.p, P};
+                    LyGemm g1{sub_in, 0, W, y.pair_row.p, lw.w_gu, (long long)GF * W, GF, W, y.gu.p, 0, GF, y.grp_off.p, P};
                     gemm_groups(lc, "gemm_moe_in", g1, E, P);
                     launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (P * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
-                           0, (const float*)nullptr, (const int*)nullptr, P, y.act.p, (uint16_t*)nullptr, (uint16_t*)nullptr);
+                           act, (const float*)nullptr, (const int*)nullptr, P, y.act.p, (uint16_t*)nullptr, (uint16_t*)nullptr);
                     LyGemm g2{y.act.p, 0, F, nullptr, lw.w_down, (long long)W * F, W, F, y.eo.p, 0, W, y.grp_off.p, P};
                     gemm_groups(lc, "gemm_moe_out", g2, E, P);
                     launch(lc, "moe_combine", 0, ly_moe_combine_kernel, gw, dim3(256), 0, (const float*)y.eo.p, (const int*)y.pair_of.p,
@@ -1063,8 +1199,13 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
                 }
             }
         }
-        launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.b_down, (const float*)lw.norm2b,
-               next1, eps, W, plain, more, y.h.p, hhi, hlo);
+        if (post)
+            launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.b_down, (const float*)lw.norm2b,
+                   next1, eps, W, plain, more, y.h.p, hhi, hlo);
+        else
+            launch(lc, "join", 0, ly_join_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)nullptr, (const float*)nullptr,
+                   (const float*)nullptr, gated ? (const float*)y.gz.p : (const float*)nullptr, (const float*)lw.rg2b, y.xs.p, hist_stride,
+                   depth ? li + 1 : -1, (const float*)lw.dwa, next1, eps, W, plain, y.h.p, hhi, hlo);
     }
     if (n_want > 0) {
         launch(lc, "final_norm", 0, ly_final_norm_kernel, dim3(n_want), dim3(nthr), 0, (const float*)y.x.p, st.want, (const float*)m.final_norm, eps, W, plain, y.hf.p,

@@ -1,7 +1,9 @@
-// Layered decoders (FL_ARCH_NIFUNEX, FL_ARCH_ROFETAR): model / cache objects shared by fl_layered.cu and fl_lib.cu.
-// A layer = one mixer (gated linear attention | latent attention | grouped-query attention | Mamba-2 | gated delta rule) + an
-// optional feed-forward (dense | MoE with shared expert), each wrapped by a norm before and after, or after only
-// (fl_stack_config.no_pre_norm).  Sizes and constants come from fl_layer_desc; nothing is fixed per model.
+// Layered decoders (FL_ARCH_NIFUNEX, FL_ARCH_ROFETAR, FL_ARCH_TOZARAX): model / cache objects shared by fl_layered.cu and fl_lib.cu.
+// A layer = one mixer (gated linear attention | latent attention | grouped-query attention | Mamba-2 | gated delta rule), or two
+// of them side by side, + an optional feed-forward (dense | MoE), each wrapped by a norm before and after, after only
+// (fl_stack_config.no_pre_norm) or before only (no_post_norm); optionally a learned position table, an input convolution in front of
+// every sublayer, a gate on every sublayer's contribution and an average over all earlier layers' outputs.  Sizes and constants
+// come from fl_layer_desc / fl_stack_config; nothing is fixed per model.
 #pragma once
 #include <cuda.h>
 
@@ -54,6 +56,19 @@ struct LayeredLayerW {
     bool tc_in = false, tc_o = false, tc_gu = false, tc_down = false, tc_sgu = false, tc_sdown = false;
     bool tc_moe = false;                               // experts: tm_gu / tm_down cover the stacked matrices (grouped GEMM, few rows),
     std::vector<CUtensorMap> tm_egu, tm_edown;         //   these one expert each (every expert over all rows, many rows)
+    float* route_corr = nullptr;        // sigmoid router: [experts] added to the scores for the choice only
+    // a second mixer beside this one: its rows follow this mixer's inside w_in (its offsets are absolute), it has its own w_o,
+    // cache / state indices and side tables; nothing but the mixer fields of it is used
+    std::shared_ptr<LayeredLayerW> side;
+    float *pair_wa = nullptr, *pair_wb = nullptr;      // [W] each: plain norm weights of the two mixers' outputs
+    // stack options
+    float *canon1 = nullptr, *canon2 = nullptr;        // [W, taps] input convolutions of the mixer / the feed-forward
+    uint16_t *rg1 = nullptr, *rg2 = nullptr;           // [W, W] gates of the two sublayers' contributions
+    float *rg1b = nullptr, *rg2b = nullptr;            // [W]
+    float* dwa = nullptr;                              // [layer index + 2] weights of the depth average
+    CUtensorMap tm_rg1{}, tm_rg2{};
+    bool tc_rg1 = false, tc_rg2 = false;
+    int canon_index = -1;               // index among the layers' input-convolution states
 };
 
 struct RopeSpec {                       // one distinct rotary configuration (tables are built per cache: they depend on max_seq)
@@ -72,9 +87,9 @@ struct LayeredModel {
     bool f32 = false;                   // compute_dtype == FL_DTYPE_F32
     std::vector<LayeredLayerW> layers;
     std::vector<RopeSpec> ropes;
-    std::vector<int> kv_layers, gla_layers;            // layers that own a paged cache (latent, or keys | values) / a recurrent state
+    std::vector<const LayeredLayerW*> kv_layers, gla_layers;   // mixers that own a paged cache (latent, or keys | values) / a recurrent state
     DevBuf<uint8_t> slab;
-    uint16_t *embed = nullptr, *head = nullptr;
+    uint16_t *embed = nullptr, *head = nullptr, *pos = nullptr;    // pos: [max_positions, W] learned position vectors (or nullptr)
     float* final_norm = nullptr;
     CUtensorMap tm_head{};
     bool tc_head = false;
@@ -96,6 +111,7 @@ struct LayeredCache {
     std::vector<DevBuf<uint8_t>> kv_store;
     std::vector<DevBuf<float>> gla_state;          // per recurrent layer: [slots][heads][dim | state][vdim]
     std::vector<DevBuf<float>> conv_state;         // per recurrent layer: [slots][taps - 1][conv_ch] (empty without a convolution)
+    std::vector<DevBuf<float>> canon_state;        // input convolutions: per layer [2 sublayers][slots][taps - 1][W]
     std::vector<DevBuf<float>> rope_cos, rope_sin; // per RopeSpec: [max_seq][dims/2]
     DevBuf<int> page_table;             // [slots][pages_per_slot]
     DevBuf<int> step_tab;               // per-step integer tables (see StepTab in fl_layered.cu)
@@ -104,6 +120,8 @@ struct LayeredCache {
     // workspace for `rows` tokens of a step
     size_t rows = 0, want_cap = 0;
     DevBuf<float> x, h, y, proj, la, u, go, qa, ol, gu, act, eo, sh_gu, sh_act, sh_o, route_w, sgate, hf, logits;
+    DevBuf<float> hc, gz, y2, xs;       // convolved sublayer input; gate pre-activations; the second mixer's projected output;
+                                        // xs [L + 1][rows][W]: the embedding output and every layer's own result (depth average)
     DevBuf<float> cv, rs;               // recurrent mixers: convolved + activated columns [rows, max_cv]; per-head (decay, strength) [rows, 2 heads]
     DevBuf<int> route_sel, pair_row, pair_of, grp_off;
     PinnedBuf<float> h_logits;

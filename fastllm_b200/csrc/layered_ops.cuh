@@ -1,8 +1,10 @@
 // Kernels of the layered decoders (sm_100a): residual / norm glue, the exact-f32 GEMM, gated linear attention (decay, scan, head
 // norm + gate), latent attention over the paged latent cache (append + rotary, absorbed-query attention), grouped-query attention
 // with per-head q/k norm, score cap and softmax sink, the short-convolution recurrent mixers (Mamba-2, gated delta rule: prep, scan,
-// gated norms), the GLU feed-forward (clamped swish or tanh-gelu, optional biases) and the mixture-of-experts router / row lists /
-// combine.  Every mechanism takes its sizes and constants as
+// gated norms), the feed-forward (clamped swish or tanh-gelu GLU with optional biases, ungated squared relu), the mixture-of-experts
+// routers (softmax top-k; sigmoid scores with a choice correction and group-limited choice) / row lists / combine, and the pieces of
+// stacks whose sublayer results join the stream un-normed (learned positions, input convolution, gated contribution, two mixers
+// side by side, depth average).  Every mechanism takes its sizes and constants as
 // arguments.  Residual stream, norms, softmax, routers, decays and the recurrent state are f32 throughout; a row's result never
 // depends on which other rows share the launch (fixed summation order per output element).
 #pragma once
@@ -72,19 +74,24 @@ static __global__ void ly_sum_slices_kernel(const float* __restrict__ y, int nsl
 // A norm weight w scales by (1 + w), or by w itself when `plain`.
 __device__ __forceinline__ float norm_scale(const float* __restrict__ w, int c, int plain) { return plain ? w[c] : 1.f + w[c]; }
 
-// x[row] = embed[tok[row]];  h[row] = x / sqrt(mean x^2 + eps) * scale(w).  nw == nullptr (the first sublayer reads the stream
-// itself): h is not written and the hi | lo halves are those of x.
+// x[row] = embed[tok[row]] (+ pos_tab[row_pos[row]], a learned position vector);  h[row] = x / sqrt(mean x^2 + eps) * scale(w).
+// nw == nullptr (the first sublayer reads the stream itself): h is not written and the hi | lo halves are those of x.
+// x0 (optional): a second copy of x, the first entry of the depth average's history.
 static __global__ void ly_embed_norm_kernel(const uint16_t* __restrict__ embed, const int* __restrict__ tok, int W, const float* __restrict__ nw,
-                                            float eps, int plain, float* __restrict__ x, float* __restrict__ h, uint16_t* __restrict__ hhi,
+                                            float eps, int plain, const uint16_t* __restrict__ pos_tab, const int* __restrict__ row_pos,
+                                            float* __restrict__ x, float* __restrict__ x0, float* __restrict__ h, uint16_t* __restrict__ hhi,
                                             uint16_t* __restrict__ hlo) {
     __shared__ float red[33];
     const int row = blockIdx.x;
     const uint16_t* e = embed + (size_t)tok[row] * W;
+    const uint16_t* pe = pos_tab ? pos_tab + (size_t)row_pos[row] * W : nullptr;
     float* xr = x + (size_t)row * W;
     float ss = 0.f;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float v = __uint_as_float((uint32_t)e[c] << 16);
+        float v = __uint_as_float((uint32_t)e[c] << 16);
+        if (pe) v += __uint_as_float((uint32_t)pe[c] << 16);
         xr[c] = v;
+        if (x0) x0[(size_t)row * W + c] = v;
         ss += v * v;
         if (nw == nullptr) split_store(hhi, hlo, (size_t)row * W + c, v);
     }
@@ -119,6 +126,55 @@ static __global__ void ly_post_norm_kernel(float* __restrict__ x, const float* _
         xr[c] = v;
         s2 += v * v;
         if (wnext == nullptr && split_x) split_store(hhi, hlo, (size_t)row * W + c, v);
+    }
+    if (wnext == nullptr) return;
+    const float r2 = 1.f / sqrtf(block_sum(s2, red) / (float)W + eps);
+    float* hr = h + (size_t)row * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = xr[c] * r2 * norm_scale(wnext, c, plain);
+        hr[c] = v;
+        split_store(hhi, hlo, (size_t)row * W + c, v);
+    }
+}
+
+// A sublayer's result joins the stream un-normed:  x[row] += gate * v,  where
+//   v = y[row], or with two mixers side by side (y2 != nullptr) v = (unit(y) * wa + unit(y2) * wb) / 2, unit(.) = . / sqrt(mean .^2 + eps);
+//   gate = sigmoid(gz[row] + gb) per channel (gz == nullptr: 1).
+// slot >= 0 (the layer's last sublayer, stacks with a depth average): hist[slot][row] = x[row], the layer's own result, and then
+//   x[row] = sum_{j <= slot} dw[j] * hist[j][row]  (hist[0] = the embedding output), in ascending j.
+// Then, if wnext, h[row] = norm(x[row]; wnext) with its hi | lo halves.
+static __global__ void ly_join_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ y2, const float* __restrict__ wa,
+                                      const float* __restrict__ wb, const float* __restrict__ gz, const float* __restrict__ gb,
+                                      float* __restrict__ hist, size_t hist_stride, int slot, const float* __restrict__ dw,
+                                      const float* __restrict__ wnext, float eps, int W, int plain, float* __restrict__ h,
+                                      uint16_t* __restrict__ hhi, uint16_t* __restrict__ hlo) {
+    __shared__ float red[33];
+    const int row = blockIdx.x;
+    const float* yr = y + (size_t)row * W;
+    const float* y2r = y2 ? y2 + (size_t)row * W : nullptr;
+    float* xr = x + (size_t)row * W;
+    float ra = 1.f, rb = 1.f;
+    if (y2r != nullptr) {
+        float sa = 0.f, sb = 0.f;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) { sa += yr[c] * yr[c]; sb += y2r[c] * y2r[c]; }
+        ra = 1.f / sqrtf(block_sum(sa, red) / (float)W + eps);
+        rb = 1.f / sqrtf(block_sum(sb, red) / (float)W + eps);
+    }
+    float s2 = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float v = yr[c];
+        if (y2r != nullptr) v = 0.5f * (v * ra * wa[c] + y2r[c] * rb * wb[c]);
+        if (gz != nullptr) v *= sigmoidf_(gz[(size_t)row * W + c] + gb[c]);
+        float t = xr[c] + v;
+        if (slot >= 0) {
+            const size_t i = (size_t)row * W + c;
+            hist[(size_t)slot * hist_stride + i] = t;
+            float acc = 0.f;
+            for (int j = 0; j < slot; ++j) acc = fmaf(dw[j], hist[(size_t)j * hist_stride + i], acc);
+            t = fmaf(dw[slot], t, acc);
+        }
+        xr[c] = t;
+        s2 += t * t;
     }
     if (wnext == nullptr) return;
     const float r2 = 1.f / sqrtf(block_sum(s2, red) / (float)W + eps);
@@ -585,7 +641,7 @@ struct AttnPrepArgs {
     int H, G, D, Dv, rdims, halves;
 };
 // Per row: every query head and (when the layer owns its cache) every key head is RMS-normed over dim with a weight shared by the
-// heads, then its first rdims channels are turned by the row's position: pairs (i, i + rdims/2) when `halves`, else (2i, 2i+1).
+// heads (qnorm == nullptr: they are used as projected), then its first rdims channels are turned by the row's position: pairs (i, i + rdims/2) when `halves`, else (2i, 2i+1).
 // Queries are rewritten in place, keys and values go to the row's cache page.  One warp per head in turn.
 template <typename CT>
 static __global__ void __launch_bounds__(128) ly_attn_prep_kernel(AttnPrepArgs a) {
@@ -608,10 +664,14 @@ static __global__ void __launch_bounds__(128) ly_attn_prep_kernel(AttnPrepArgs a
         const bool isq = it < a.H;
         float* src = isq ? pr + a.off_q + it * a.D : pr + a.off_k + (it - a.H) * a.D;
         const float* w = isq ? a.qnorm : a.knorm;
-        float ss = 0.f;
-        for (int c = lane; c < a.D; c += 32) ss += src[c] * src[c];
-        const float r = 1.f / sqrtf(warp_sum(ss) / (float)a.D + a.eps);
-        for (int c = lane; c < a.D; c += 32) buf[c] = src[c] * r * w[c];
+        if (w != nullptr) {
+            float ss = 0.f;
+            for (int c = lane; c < a.D; c += 32) ss += src[c] * src[c];
+            const float r = 1.f / sqrtf(warp_sum(ss) / (float)a.D + a.eps);
+            for (int c = lane; c < a.D; c += 32) buf[c] = src[c] * r * w[c];
+        } else {
+            for (int c = lane; c < a.D; c += 32) buf[c] = src[c];
+        }
         __syncwarp();
         for (int c = lane; c < a.D; c += 32) {
             float val = buf[c];
@@ -858,6 +918,20 @@ static __global__ void ly_conv_state_kernel(ConvArgs a) {
     for (int i = 0; i < a.taps - 1; ++i) a.state[((size_t)slot * (a.taps - 1) + i) * a.ch + c] = keep[i];
 }
 
+// The input convolution in front of a sublayer: out[row, c] = in[row, c] + sum_k w[c, k] * in[position - (taps - 1 - k), c] (no bias,
+// no activation; a.proj / a.off name `in`), with its hi | lo halves.  grid (rows, channel blocks).
+static __global__ void ly_input_conv_kernel(ConvArgs a, float* __restrict__ out, uint16_t* __restrict__ ohi, uint16_t* __restrict__ olo) {
+    const int row = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= a.ch) return;
+    const int seq = a.row_seq[row], pos = a.row_pos[row];
+    const int row0 = a.seq_row0[seq], pos0 = a.seq_pos0[seq], slot = a.seq_slot[seq];
+    float t = 0.f;
+    for (int k = 0; k < a.taps; ++k) t = fmaf(a.w[(size_t)c * a.taps + k], conv_input(a, row, row0, pos, pos0, slot, a.taps - 1 - k, c), t);
+    t += a.proj[(size_t)row * a.ldp + a.off + c];
+    out[(size_t)row * a.ch + c] = t;
+    split_store(ohi, olo, (size_t)row * a.ch + c, t);
+}
+
 // Mamba-2, per row: x | B | C <- silu(conv + bias);  per head  b = softplus(dt + dt_bias),  a = exp(-exp(A_log) b)  -> ab[row, h] = (a, b).
 // grid (rows, channel chunks of `chunk`): the first chunk's block also computes the per-head scalars.
 static __global__ void ly_mamba_prep_kernel(ConvArgs a, int chunk, int off_dt, const float* __restrict__ dt_bias, const float* __restrict__ a_log, int H,
@@ -1043,8 +1117,9 @@ static __global__ void ly_gated_group_norm_kernel(const float* __restrict__ y, c
 // ---- feed-forward ----------------------------------------------------------------------------------------------------------
 // act 0: act[p, f] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[p, f], limit),  u = clamp(gu[p, F + f], -limit, limit);
 // act 1: act[p, f] = gelu_tanh(g) * u,  gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  bias [2F] (optional) is added
-// to gate | up first.  p < *count
+// to gate | up first.  act 2: act[p, f] = relu(gu[p, f])^2 -- no gate matrix, gu has F columns.  p < *count
 __device__ __forceinline__ float glu_value(float g, float u, int act, float limit) {
+    if (act == 2) { g = fmaxf(g, 0.f); return g * g; }
     if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
@@ -1057,8 +1132,9 @@ static __global__ void ly_glu_kernel(const float* __restrict__ gu, int F, float 
     const size_t total = (size_t)n * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t p = i / F, f = i - p * F;
-        const float g = gu[p * 2 * F + f] + (bias ? bias[f] : 0.f);
-        const float u = gu[p * 2 * F + F + f] + (bias ? bias[F + f] : 0.f);
+        const size_t gs = act_kind == 2 ? (size_t)F : (size_t)2 * F;
+        const float g = gu[p * gs + f] + (bias ? bias[f] : 0.f);
+        const float u = act_kind == 2 ? 0.f : gu[p * gs + F + f] + (bias ? bias[F + f] : 0.f);
         const float v = glu_value(g, u, act_kind, limit);
         if (act != nullptr) act[i] = v;         // nullptr: only the hi | lo halves are consumed (a tensor-core GEMM follows)
         split_store(ahi, alo, i, v);
@@ -1114,6 +1190,67 @@ static __global__ void ly_router_kernel(const float* __restrict__ h, int W, cons
     }
 }
 
+// Router with independent scores: z = Wr h (f32), s = sigmoid(z); the choice runs on c = s + corr.  The experts form `groups` equal
+// groups of neighbours; a group's mark is the sum of its two largest c (its only one, for groups of one); the `keep` groups with the
+// largest marks stay eligible, the others' experts cannot be chosen whatever their c (c may be negative); the `top` eligible experts
+// with the largest c are used with the weights s, as they are.  Lower index first among equals, everywhere.
+// One block per row, one warp per expert in turn; shared memory: 2 E + groups floats.
+static __global__ void ly_router_sigmoid_kernel(const float* __restrict__ h, int W, const float* __restrict__ wr, int E, int top,
+                                                const float* __restrict__ corr, int groups, int keep, int* __restrict__ sel,
+                                                float* __restrict__ wt) {
+    extern __shared__ float z[];                 // [E] scores s, [E] choice scores c, [groups] marks
+    float* cc = z + E;
+    float* mark = cc + E;
+    const int row = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float* hr = h + (size_t)row * W;
+    for (int e = wid; e < E; e += nw) {
+        const float* w = wr + (size_t)e * W;
+        float d = 0.f;
+        if ((W & 3) == 0) {
+            const float4* w4 = reinterpret_cast<const float4*>(w);
+            const float4* h4 = reinterpret_cast<const float4*>(hr);
+            for (int c = lane; c < W / 4; c += 32) {
+                const float4 a = w4[c], b = h4[c];
+                d = fmaf(a.x, b.x, d); d = fmaf(a.y, b.y, d); d = fmaf(a.z, b.z, d); d = fmaf(a.w, b.w, d);
+            }
+        } else {
+            for (int c = lane; c < W; c += 32) d = fmaf(w[c], hr[c], d);
+        }
+        d = warp_sum(d);
+        if (lane == 0) { const float s = sigmoidf_(d); z[e] = s; cc[e] = s + corr[e]; }
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    const int per = E / groups;
+    for (int g = 0; g < groups; ++g) {
+        float b1 = -INFINITY, b2 = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+            const float v = cc[e];
+            if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) b2 = v;
+        }
+        mark[g] = per > 1 ? b1 + b2 : b1;
+    }
+    // drop the groups.count - keep groups with the smallest marks (higher index first among equals): what stays is the `keep` best
+    for (int k = 0; k < groups - keep; ++k) {
+        int worst = -1;
+        float wv = INFINITY;
+        for (int g = 0; g < groups; ++g)
+            if (mark[g] != INFINITY && (worst < 0 || mark[g] <= wv)) { wv = mark[g]; worst = g; }
+        mark[worst] = INFINITY;                  // a dropped group
+        for (int e = worst * per; e < (worst + 1) * per; ++e) cc[e] = -INFINITY;
+    }
+    for (int k = 0; k < top; ++k) {
+        int best = -1;
+        float bv = -INFINITY;
+        for (int e = 0; e < E; ++e)
+            if (cc[e] > bv) { bv = cc[e]; best = e; }
+        if (best < 0) best = 0;                  // only with scores that are not numbers
+        sel[row * top + k] = best;
+        wt[row * top + k] = z[best];
+        cc[best] = -INFINITY;
+    }
+}
+
 // Row lists per expert, in ascending (row, pick) order: grp_off[E + 1], pair_row[p] = source row, pair_of[row * top + k] = p.
 // One warp per expert (grid = E blocks of 32 threads): a first sweep counts the picks of lower experts (the list's offset) and
 // its own, a second places its picks by ballot compaction -- stable, so the lists do not depend on timing.
@@ -1159,17 +1296,20 @@ static __global__ void ly_moe_gather_kernel(const uint16_t* __restrict__ hhi, co
         for (int c = threadIdx.x; c < W; c += blockDim.x) { gx_hi[dst + c] = hhi[src + c]; gx_lo[dst + c] = hlo[src + c]; }
     }
 }
-// The clamped GLU over the grouped GEMM's output: gu[slice][e * cap + i][2F] summed over slices, rows i < cnt[e] only -> hi | lo.
-static __global__ void ly_glu_grouped_kernel(const float* __restrict__ gu, int nsl, size_t sl_stride, int F, float limit, const int* __restrict__ cnt,
-                                             int cap, uint16_t* __restrict__ ahi, uint16_t* __restrict__ alo) {
+// The activation over the grouped GEMM's output: gu[slice][e * cap + i][2F] (F columns for the ungated act 2) summed over slices, rows
+// i < cnt[e] only -> hi | lo.
+static __global__ void ly_glu_grouped_kernel(const float* __restrict__ gu, int nsl, size_t sl_stride, int F, float limit, int act_kind,
+                                             const int* __restrict__ cnt, int cap, uint16_t* __restrict__ ahi, uint16_t* __restrict__ alo) {
     const int r = blockIdx.y;                   // row e * cap + i
     if (r % cap >= cnt[r / cap]) return;
     for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < F; f += gridDim.x * blockDim.x) {
         float g = 0.f, u = 0.f;
-        for (int k = 0; k < nsl; ++k) { g += gu[k * sl_stride + (size_t)r * 2 * F + f]; u += gu[k * sl_stride + (size_t)r * 2 * F + F + f]; }
-        g = fminf(g, limit);
-        u = fminf(fmaxf(u, -limit), limit);
-        split_store(ahi, alo, (size_t)r * F + f, g * sigmoidf_(1.702f * g) * (u + 1.f));
+        const size_t gs = act_kind == 2 ? (size_t)F : (size_t)2 * F;
+        for (int k = 0; k < nsl; ++k) {
+            g += gu[k * sl_stride + (size_t)r * gs + f];
+            if (act_kind != 2) u += gu[k * sl_stride + (size_t)r * gs + F + f];
+        }
+        split_store(ahi, alo, (size_t)r * F + f, glu_value(g, u, act_kind, limit));
     }
 }
 // y[row, c] = sum_k wt[row, k] * (sum over slices of eo[slice][block row of (row, k)][c]) + sgate[row] * sh[row, c]

@@ -544,6 +544,11 @@ class _LayeredBase(_CausalBase):
     POOL_TOKENS = None          # None: room for MAX_BATCH x capacity tokens
     norm_plain = False          # layer norms and the final norm scale by w instead of 1 + w
     no_pre_norm = False         # sublayers read the residual stream itself; only their outputs are normed
+    no_post_norm = False        # a sublayer's result joins the residual stream as it is
+
+    @classmethod
+    def stack_options(cls, config: dict, sc) -> None:
+        """fills the stack-wide options of a FlStackConfig that the design reads from config.json (none by default)"""
 
     def __init__(self, dev: DeviceModel, cfg, config: dict):
         super().__init__(dev, cfg)
@@ -569,7 +574,8 @@ class _LayeredBase(_CausalBase):
         sc.vocab, sc.width, sc.n_layers = int(config["vocab"]), int(config["width"]), len(config["layers"])
         sc.norm_eps = float(config["norm"]["eps"])
         sc.compute_dtype = _lib.FL_DTYPE_F32 if dtype in ("f32", "float32") else _lib.FL_DTYPE_BF16
-        sc.norm_plain, sc.no_pre_norm = int(cls.norm_plain), int(cls.no_pre_norm)
+        sc.norm_plain, sc.no_pre_norm, sc.no_post_norm = int(cls.norm_plain), int(cls.no_pre_norm), int(cls.no_post_norm)
+        cls.stack_options(config, sc)
         dev = DeviceModel(sc, device, layers=cls.layer_descs(config, shapes, **hints))
         if items is None:
             dev.random_init(0 if random_seed is None else random_seed, std)
@@ -665,9 +671,77 @@ class RofetarWithConfig(_LayeredBase):
         return rofetar_layer_descs(config)
 
 
+def _attention_desc(d, m: dict):
+    """fills the fields of a plain grouped-query attention mixer (no q/k norm, no rotation unless 'rot' says so, optional window)"""
+    d.mixer = _lib.FL_MIXER["attention"]
+    d.heads, d.dim, d.vdim = int(m["heads"]), int(m["dim"]), int(m["vdim"])
+    d.kv_heads, d.kv_from = int(m.get("kv_heads") or m["heads"]), -1
+    d.scale = float(m["scale"])
+    d.window = int((m.get("mask") or {}).get("size") or 0)
+    d.no_qk_norm, d.rot_halves = 1, 1
+    _rotary_desc(d, m.get("rot") or {"dims": 0}, 0)
+
+
+def _delta_desc(d, m: dict):
+    """fills the fields of a gated-delta-rule mixer"""
+    d.mixer = _lib.FL_MIXER["delta"]
+    d.heads, d.dim, d.vdim = int(m["heads"]), int(m["dim"]), int(m["vdim"])
+    d.kv_heads, d.conv, d.kv_from = int(m.get("kv_heads") or m["heads"]), int(m["conv"]), -1
+
+
+def tozarax_layer_descs(config: dict):
+    """config.json of the Tozarax decoder -> ctypes array of FlLayerDesc: two descriptors per layer (the attention mixer with the
+    layer's feed-forward, then the delta-rule mixer that runs beside it).  Every size and constant comes from the file."""
+    layers = config["layers"]
+    arr = (_lib.FlLayerDesc * (2 * len(layers)))()
+    for i, l in enumerate(layers):
+        if l["type"] != "parallel":
+            raise FastllmError(-1, f"layer {i}: unknown mixer type {l['type']!r}")
+        a, b = arr[2 * i], arr[2 * i + 1]
+        _attention_desc(a, l["mixer"]["left"])
+        a.beside = 1
+        _delta_desc(b, l["mixer"]["right"])
+        mlp = l.get("mlp")
+        if not mlp:
+            a.ffn = _lib.FL_FFN["none"]
+            continue
+        if mlp["kind"] != "moe":
+            raise FastllmError(-1, f"layer {i}: unknown feed-forward kind {mlp['kind']!r}")
+        r = mlp["router"]
+        a.ffn, a.ffn_act, a.ff = _lib.FL_FFN["moe"], _lib.FL_ACT["relu2"], int(mlp["expert"]["ff"])
+        a.experts, a.top = int(r["experts"]), int(r["top"])
+        a.router = _lib.FL_ROUTER["sigmoid_groups"]
+        g = r.get("groups") or {}
+        a.route_groups = int(g.get("count") or 1)
+        a.route_keep = int(g.get("keep") or a.route_groups)
+    return arr
+
+
+class TozaraxWithConfig(_LayeredBase):
+    """The Tozarax decoder (no reference path): learned positions; every layer runs a windowed softmax attention without rotation
+    beside a gated delta rule (each output normed, the two averaged) and a sigmoid-routed mixture of squared-relu experts with
+    group-limited choice; sublayers are pre-normed, read their input through a short causal convolution, scale their contribution
+    by a learned gate, and every layer hands on a learned average of all layers' outputs so far."""
+    arch, family, architectures = "tozarax", "Tozarax", ("Tozarax",)
+    no_post_norm = True
+
+    @classmethod
+    def stack_options(cls, config: dict, sc) -> None:
+        sc.max_positions = int(config["max_positions"])
+        sc.canon_taps = int((config.get("canon") or {}).get("taps") or 0)
+        sc.gated_residual, sc.depth_avg = 1, 1
+
+    @classmethod
+    def layer_descs(cls, config: dict, tensor_shapes: dict):
+        return tozarax_layer_descs(config)
+
+    def _capacity(self) -> int:
+        return min(self.KV_CAPACITY, int(self.config["max_positions"]))
+
+
 # every adapter, in the order the registry tries them (model_registry.rs:169-182 keeps the same kind of list)
 def registered_models():
-    return (LlamaWithConfig, MistralWithConfig, QwenWithConfig, MixtralWithConfig, NifunexWithConfig, RofetarWithConfig)
+    return (LlamaWithConfig, MistralWithConfig, QwenWithConfig, MixtralWithConfig, NifunexWithConfig, RofetarWithConfig, TozaraxWithConfig)
 
 
 def model_class_for(config: dict):

@@ -70,8 +70,11 @@ typedef enum fl_arch {
     FL_ARCH_BERT = 4,      /* BertModel encoder         (models/embeddings.rs) */
     FL_ARCH_NIFUNEX = 5,   /* layered decoder described by fl_layer_desc (no reference path): gated-linear-attention and windowed
                               latent-attention mixers, dense / mixture-of-experts feed-forward, a norm before and after each sublayer */
-    FL_ARCH_ROFETAR = 6    /* layered decoder (no reference path): grouped-query attention with a softmax sink, Mamba-2 and gated-delta-rule
+    FL_ARCH_ROFETAR = 6,   /* layered decoder (no reference path): grouped-query attention with a softmax sink, Mamba-2 and gated-delta-rule
                               mixers, biased gelu feed-forward; only the OUTPUT of a sublayer is normed (fl_stack_config.no_pre_norm) */
+    FL_ARCH_TOZARAX = 7    /* layered decoder (no reference path): learned positions; pre-normed sublayers that read their input through a
+                              short causal convolution, gate their contribution and average over all earlier layers' outputs; two mixers
+                              side by side (windowed attention without rotation | gated delta rule); sigmoid-routed squared-relu experts */
 } fl_arch;
 
 typedef enum fl_dtype { FL_DTYPE_F32 = 0, FL_DTYPE_BF16 = 1, FL_DTYPE_F16 = 2 } fl_dtype;
@@ -130,11 +133,18 @@ typedef struct fl_config {
  * The recurrent mixers keep, per sequence slot, the state S and the last conv - 1 inputs of every convolved channel.
  * Feed-forward (ffn_act = FL_ACT_SWISH_CLAMP): y = W_down (g * sigmoid(1.702 g) * (u + 1)), g = min(W_gate h, limit), u = clamp(W_up h,
  * -limit, limit); (ffn_act = FL_ACT_GELU_TANH): y = W_down (gelu_tanh(W_gate h) * (W_up h)); ffn_bias adds a bias to all three
- * projections.  Dense, or `top` of `experts` such experts weighted by their renormalised softmax scores plus an optional always-on
- * shared expert scaled by sigmoid(w_sg . h). */
+ * projections; (ffn_act = FL_ACT_RELU2): y = W_down relu(W_up h)^2, no gate matrix.  Dense, or `top` of `experts` such experts
+ * weighted by their renormalised softmax scores plus an optional always-on shared expert scaled by sigmoid(w_sg . h)
+ * (router = FL_ROUTER_SOFTMAX); or (router = FL_ROUTER_SIGMOID_GROUPS) scores s = sigmoid(W_r h), choice scores s + correction, the
+ * experts form `route_groups` equal groups of neighbours of which the `route_keep` with the largest sum of their two best choice
+ * scores stay eligible, the `top` eligible experts with the largest choice scores are used with weights s (not renormalised).
+ * Two mixers side by side (`beside`): both read the layer's mixer input; the layer's mixer output is half the sum of the two
+ * outputs, each RMS-normed over the width with a plain weight ("l<i>.mix.left.out" / "l<i>.mix.right.out"); their tensors are
+ * "l<i>.mix.left.*" / "l<i>.mix.right.*". */
 typedef enum fl_mixer_kind { FL_MIXER_GLA = 0, FL_MIXER_LATENT_ATTN = 1, FL_MIXER_ATTN = 2, FL_MIXER_MAMBA2 = 3, FL_MIXER_DELTA = 4 } fl_mixer_kind;
 typedef enum fl_ffn_kind { FL_FFN_NONE = 0, FL_FFN_DENSE = 1, FL_FFN_MOE = 2 } fl_ffn_kind;
-typedef enum fl_ffn_act { FL_ACT_SWISH_CLAMP = 0, FL_ACT_GELU_TANH = 1 } fl_ffn_act;
+typedef enum fl_ffn_act { FL_ACT_SWISH_CLAMP = 0, FL_ACT_GELU_TANH = 1, FL_ACT_RELU2 = 2 } fl_ffn_act;
+typedef enum fl_router_kind { FL_ROUTER_SOFTMAX = 0, FL_ROUTER_SIGMOID_GROUPS = 1 } fl_router_kind;
 
 typedef struct fl_layer_desc {
     int32_t mixer;                     /* fl_mixer_kind */
@@ -161,8 +171,13 @@ typedef struct fl_layer_desc {
     float softcap;                     /* attention: score <- softcap * tanh(score / softcap); 0 = none */
     int32_t sink;                      /* attention: 1 = one is added to the softmax denominator */
     int32_t rot_halves;                /* attention: 1 = rotary pairs are (i, i + rot_dims / 2), 0 = (2i, 2i + 1) */
-    int32_t ffn_act, ffn_bias;         /* dense feed-forward: fl_ffn_act; 1 = gate / up / down carry biases */
-    int32_t reserved[6];
+    int32_t ffn_act, ffn_bias;         /* feed-forward: fl_ffn_act; dense: 1 = gate / up / down carry biases */
+    int32_t no_qk_norm;                /* attention: 1 = queries and keys are used as projected (no per-head norm, no norm tensors) */
+    int32_t beside;                    /* 1 = the NEXT descriptor of the array describes a second mixer of this layer (its mixer fields only;
+                                          it counts as no layer of its own); attention or delta rule, each with its own cache / state */
+    int32_t router;                    /* MoE: fl_router_kind */
+    int32_t route_groups, route_keep;  /* FL_ROUTER_SIGMOID_GROUPS: groups of neighbouring experts / groups that stay eligible */
+    int32_t reserved[1];
 } fl_layer_desc;
 
 typedef struct fl_stack_config {
@@ -174,7 +189,16 @@ typedef struct fl_stack_config {
     int32_t norm_plain;                /* 0: the layer norms and the final norm scale by (1 + w);  1: by w */
     int32_t no_pre_norm;               /* 0: x += norm_b(sub(norm_a(x)));  1: x += norm(sub(x)) -- sublayers read the residual stream itself
                                           and "l<i>.norm1" / "l<i>.norm2" name the norms of the mixer's / feed-forward's output */
-    int32_t reserved[4];
+    int32_t no_post_norm;              /* 1: x += sub(norm_a(x)) -- a sublayer's result joins the stream as it is (needs pre-norms) */
+    int32_t max_positions;             /* > 0: a learned position vector "pos" [max_positions, width] is added to the embedding */
+    int32_t canon_taps;                /* > 0: every sublayer reads h + conv(h) instead of its input h, a causal per-channel convolution of
+                                          this many taps ("l<i>.canon1" / "canon2" [width, taps], last column = the current token); the last
+                                          taps - 1 inputs are kept per sequence slot */
+    int32_t gated_residual;            /* 1: a sublayer's result is multiplied by sigmoid(W h + b) ("l<i>.rg1|rg2" [width, width], ".b"),
+                                          h = the sublayer's normed input before the convolution */
+    int32_t depth_avg;                 /* 1: what leaves layer i is sum_j dwa[j] X_j over X_0 = the embedding output and X_j+1 = layer j's own
+                                          result, j <= i ("l<i>.dwa" [i + 2]) */
+    int32_t reserved[3];
 } fl_stack_config;
 
 /* ---- process / device -------------------------------------------------------------------------- */
@@ -185,7 +209,7 @@ FL_EXPORT int fl_device_synchronize(void);
 
 /* ---- model (weights) --------------------------------------------------------------------------- */
 FL_EXPORT int fl_model_create(const fl_config* cfg, fl_model** out);
-/* A layered model: cfg->n_layers entries of `layers`.  Tensors then arrive by name through fl_model_put_tensor ("embed", "head",
+/* A layered model: cfg->n_layers entries of `layers` (plus one more after every entry with `beside` set).  Tensors then arrive by name through fl_model_put_tensor ("embed", "head",
  * "final.norm", "l<i>.norm1|norm1b|norm2|norm2b" (no_pre_norm: "l<i>.norm1|norm2"), "l<i>.mix.*", "l<i>.mlp.*"); fl_model_finalize
  * checks that all came. */
 FL_EXPORT int fl_model_create_layered(const fl_stack_config* cfg, const fl_layer_desc* layers, fl_model** out);
