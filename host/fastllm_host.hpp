@@ -292,15 +292,21 @@ struct LayeredModel {
     fl_model* h = nullptr;
     fl_stack_config cfg{};
     std::vector<fl_layer_desc> layers;
+    // a descriptor with `beside` set is followed by the descriptor of the layer's second mixer, which counts as no layer of its own
+    static int32_t count_layers(const std::vector<fl_layer_desc>& l) {
+        int32_t n = (int32_t)l.size();
+        for (const fl_layer_desc& d : l) n -= d.beside ? 1 : 0;
+        return n;
+    }
     LayeredModel(const fl_stack_config& c, std::vector<fl_layer_desc> l, const TensorMap& tensors) : cfg(c), layers(std::move(l)) {
-        cfg.n_layers = (int32_t)layers.size();
+        cfg.n_layers = count_layers(layers);
         check(fl_model_create_layered(&cfg, layers.data(), &h));
         for (const auto& kv : tensors)
             check(fl_model_put_tensor(h, kv.first.c_str(), kv.second.dtype, kv.second.shape.data(), (int)kv.second.shape.size(), kv.second.data));
         check(fl_model_finalize(h));
     }
     LayeredModel(const fl_stack_config& c, std::vector<fl_layer_desc> l, uint64_t seed, float std_dev) : cfg(c), layers(std::move(l)) {   // synthetic weights
-        cfg.n_layers = (int32_t)layers.size();
+        cfg.n_layers = count_layers(layers);
         check(fl_model_create_layered(&cfg, layers.data(), &h));
         check(fl_model_random_init(h, seed, std_dev));
         check(fl_model_finalize(h));
