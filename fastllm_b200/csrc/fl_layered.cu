@@ -1103,9 +1103,26 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
             const int taps = m.cfg.canon_taps;
             float* cs = taps > 1 ? y.canon_state[lw.canon_index].p + (size_t)sub * c.max_batch * (taps - 1) * W : nullptr;
             ConvArgs ca{norm_out, W, 0, sub == 0 ? lw.canon1 : lw.canon2, nullptr, cs, st.row_seq, st.row_pos, st.seq_row0, st.seq_slot, st.seq_pos0, W, taps, nullptr};
-            launch(lc, "input_conv", 0, ly_input_conv_kernel, dim3(Ti, (W + 255) / 256), dim3(256), 0, ca, y.hc.p, hhi, hlo);
+            // few rows: one row per block; long steps: a block walks 8 rows with its taps staged once
+            const int rpb = Ti >= 1024 ? 8 : 1;
+            if (W % 4 == 0)
+                launch(lc, "input_conv", 0, ly_input_conv_kernel<4>, dim3((Ti + rpb - 1) / rpb, (W / 4 + 127) / 128), dim3(128), (size_t)taps * 128 * 4 * 4, ca, rpb, Ti,
+                       y.hc.p, hhi, hlo);
+            else
+                launch(lc, "input_conv", 0, ly_input_conv_kernel<1>, dim3((Ti + rpb - 1) / rpb, (W + 127) / 128), dim3(128), (size_t)taps * 128 * 4, ca, rpb, Ti,
+                       y.hc.p, hhi, hlo);
             if (taps > 1) launch(lc, "conv_state", 0, ly_conv_state_kernel, dim3(n, (W + 127) / 128), dim3(128), 0, ca);
         }
+    };
+    // a sublayer's result (y.y, and y2 beside it) joins the stream; four channels per thread when the rows are 16-byte multiples
+    auto join = [&](const float* y2, const float* wa, const float* wb, const float* gate_bias, int hist_slot, const float* dw, const float* wnext) {
+        const float* gz = gated ? (const float*)y.gz.p : (const float*)nullptr;
+        if (W % 4 == 0)
+            launch(lc, "join", 0, ly_join_kernel<4>, dim3(Ti), dim3(std::min(256, std::max(32, (W / 4 + 31) / 32 * 32))), 0, y.x.p, (const float*)y.y.p, y2, wa, wb,
+                   gz, gate_bias, y.xs.p, hist_stride, hist_slot, dw, wnext, eps, W, plain, y.h.p, hhi, hlo);
+        else
+            launch(lc, "join", 0, ly_join_kernel<1>, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, y2, wa, wb, gz, gate_bias, y.xs.p, hist_stride,
+                   hist_slot, dw, wnext, eps, W, plain, y.h.p, hhi, hlo);
     };
     for (int li = 0; li < m.L; ++li) {
         const LayeredLayerW& lw = m.layers[li];
@@ -1127,10 +1144,8 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
             launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)nullptr, (const float*)lw.norm1b,
                    has_ff ? (const float*)lw.norm2 : next1, eps, W, plain, has_ff ? split_x : more, y.h.p, hhi, hlo);
         else
-            launch(lc, "join", 0, ly_join_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, lw.side ? (const float*)y.y2.p : (const float*)nullptr,
-                   (const float*)lw.pair_wa, (const float*)lw.pair_wb, gated ? (const float*)y.gz.p : (const float*)nullptr, (const float*)lw.rg1b,
-                   y.xs.p, hist_stride, (depth && !has_ff) ? li + 1 : -1, (const float*)lw.dwa, has_ff ? (const float*)lw.norm2 : next1, eps, W, plain,
-                   y.h.p, hhi, hlo);
+            join(lw.side ? (const float*)y.y2.p : (const float*)nullptr, lw.pair_wa, lw.pair_wb, lw.rg1b, (depth && !has_ff) ? li + 1 : -1, lw.dwa,
+                 has_ff ? (const float*)lw.norm2 : next1);
         if (!has_ff) continue;
         sublayer_front(lw, 1);
         const int F = d.ff, act = d.ffn_act, GF = act == FL_ACT_RELU2 ? F : 2 * F;
@@ -1203,9 +1218,7 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
             launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.b_down, (const float*)lw.norm2b,
                    next1, eps, W, plain, more, y.h.p, hhi, hlo);
         else
-            launch(lc, "join", 0, ly_join_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)nullptr, (const float*)nullptr,
-                   (const float*)nullptr, gated ? (const float*)y.gz.p : (const float*)nullptr, (const float*)lw.rg2b, y.xs.p, hist_stride,
-                   depth ? li + 1 : -1, (const float*)lw.dwa, next1, eps, W, plain, y.h.p, hhi, hlo);
+            join(nullptr, nullptr, nullptr, lw.rg2b, depth ? li + 1 : -1, lw.dwa, next1);
     }
     if (n_want > 0) {
         launch(lc, "final_norm", 0, ly_final_norm_kernel, dim3(n_want), dim3(nthr), 0, (const float*)y.x.p, st.want, (const float*)m.final_norm, eps, W, plain, y.hf.p,

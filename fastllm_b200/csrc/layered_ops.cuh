@@ -61,6 +61,40 @@ __device__ __forceinline__ void split_store(uint16_t* hi, uint16_t* lo, size_t i
 static __global__ void ly_split_kernel(const float* __restrict__ x, size_t n, uint16_t* __restrict__ hi, uint16_t* __restrict__ lo) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) split_store(hi, lo, i, x[i]);
 }
+// V consecutive floats at once (V = 4: one 16-byte access; the address must be 16-byte aligned) and their hi | lo halves
+template <int V>
+__device__ __forceinline__ void ld_vec(const float* p, float (&o)[V]) {
+    if constexpr (V == 4) { const float4 t = *reinterpret_cast<const float4*>(p); o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w; }
+    else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) o[i] = p[i];
+    }
+}
+template <int V>
+__device__ __forceinline__ void st_vec(float* p, const float (&o)[V]) {
+    if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+    else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) p[i] = o[i];
+    }
+}
+template <int V>
+__device__ __forceinline__ void split_store_vec(uint16_t* hi, uint16_t* lo, size_t i, const float (&o)[V]) {
+    if (hi == nullptr) return;
+    uint16_t h[V], l[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+        h[k] = f32_to_bf16_rne(o[k]);
+        l[k] = f32_to_bf16_rne(o[k] - __uint_as_float((uint32_t)h[k] << 16));
+    }
+    if constexpr (V == 4) {
+        *reinterpret_cast<uint2*>(hi + i) = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+        *reinterpret_cast<uint2*>(lo + i) = make_uint2((uint32_t)l[0] | ((uint32_t)l[1] << 16), (uint32_t)l[2] | ((uint32_t)l[3] << 16));
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) { hi[i + k] = h[k]; lo[i + k] = l[k]; }
+    }
+}
 // out[i] = sum over the split-K slices of a tensor-core GEMM, in slice order
 static __global__ void ly_sum_slices_kernel(const float* __restrict__ y, int nsl, size_t stride, size_t n, float* __restrict__ out) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -143,6 +177,8 @@ static __global__ void ly_post_norm_kernel(float* __restrict__ x, const float* _
 // slot >= 0 (the layer's last sublayer, stacks with a depth average): hist[slot][row] = x[row], the layer's own result, and then
 //   x[row] = sum_{j <= slot} dw[j] * hist[j][row]  (hist[0] = the embedding output), in ascending j.
 // Then, if wnext, h[row] = norm(x[row]; wnext) with its hi | lo halves.
+// One block per row; a thread takes V consecutive channels at a time (V = 4: 16-byte accesses, W a multiple of 4).
+template <int V>
 static __global__ void ly_join_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ y2, const float* __restrict__ wa,
                                       const float* __restrict__ wb, const float* __restrict__ gz, const float* __restrict__ gb,
                                       float* __restrict__ hist, size_t hist_stride, int slot, const float* __restrict__ dw,
@@ -150,39 +186,68 @@ static __global__ void ly_join_kernel(float* __restrict__ x, const float* __rest
                                       uint16_t* __restrict__ hhi, uint16_t* __restrict__ hlo) {
     __shared__ float red[33];
     const int row = blockIdx.x;
-    const float* yr = y + (size_t)row * W;
-    const float* y2r = y2 ? y2 + (size_t)row * W : nullptr;
-    float* xr = x + (size_t)row * W;
-    float ra = 1.f, rb = 1.f;
-    if (y2r != nullptr) {
+    const size_t rb = (size_t)row * W;
+    const int step = blockDim.x * V;
+    float ra = 1.f, rb2 = 1.f;
+    if (y2 != nullptr) {
         float sa = 0.f, sb = 0.f;
-        for (int c = threadIdx.x; c < W; c += blockDim.x) { sa += yr[c] * yr[c]; sb += y2r[c] * y2r[c]; }
+        for (int c = threadIdx.x * V; c < W; c += step) {
+            float p[V], q[V];
+            ld_vec<V>(y + rb + c, p); ld_vec<V>(y2 + rb + c, q);
+#pragma unroll
+            for (int i = 0; i < V; ++i) { sa += p[i] * p[i]; sb += q[i] * q[i]; }
+        }
         ra = 1.f / sqrtf(block_sum(sa, red) / (float)W + eps);
-        rb = 1.f / sqrtf(block_sum(sb, red) / (float)W + eps);
+        rb2 = 1.f / sqrtf(block_sum(sb, red) / (float)W + eps);
     }
     float s2 = 0.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        float v = yr[c];
-        if (y2r != nullptr) v = 0.5f * (v * ra * wa[c] + y2r[c] * rb * wb[c]);
-        if (gz != nullptr) v *= sigmoidf_(gz[(size_t)row * W + c] + gb[c]);
-        float t = xr[c] + v;
-        if (slot >= 0) {
-            const size_t i = (size_t)row * W + c;
-            hist[(size_t)slot * hist_stride + i] = t;
-            float acc = 0.f;
-            for (int j = 0; j < slot; ++j) acc = fmaf(dw[j], hist[(size_t)j * hist_stride + i], acc);
-            t = fmaf(dw[slot], t, acc);
+    for (int c = threadIdx.x * V; c < W; c += step) {
+        float v[V], t[V];
+        ld_vec<V>(y + rb + c, v);
+        if (y2 != nullptr) {
+            float q[V], fa[V], fb[V];
+            ld_vec<V>(y2 + rb + c, q); ld_vec<V>(wa + c, fa); ld_vec<V>(wb + c, fb);
+#pragma unroll
+            for (int i = 0; i < V; ++i) v[i] = 0.5f * (v[i] * ra * fa[i] + q[i] * rb2 * fb[i]);
         }
-        xr[c] = t;
-        s2 += t * t;
+        if (gz != nullptr) {
+            float z[V], bz[V];
+            ld_vec<V>(gz + rb + c, z); ld_vec<V>(gb + c, bz);
+#pragma unroll
+            for (int i = 0; i < V; ++i) v[i] *= sigmoidf_(z[i] + bz[i]);
+        }
+        ld_vec<V>(x + rb + c, t);
+#pragma unroll
+        for (int i = 0; i < V; ++i) t[i] += v[i];
+        if (slot >= 0) {
+            st_vec<V>(hist + (size_t)slot * hist_stride + rb + c, t);
+            float acc[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] = 0.f;
+            for (int j = 0; j < slot; ++j) {
+                float o[V];
+                ld_vec<V>(hist + (size_t)j * hist_stride + rb + c, o);
+                const float dj = dw[j];
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] = fmaf(dj, o[i], acc[i]);
+            }
+            const float ds = dw[slot];
+#pragma unroll
+            for (int i = 0; i < V; ++i) t[i] = fmaf(ds, t[i], acc[i]);
+        }
+        st_vec<V>(x + rb + c, t);
+#pragma unroll
+        for (int i = 0; i < V; ++i) s2 += t[i] * t[i];
     }
     if (wnext == nullptr) return;
     const float r2 = 1.f / sqrtf(block_sum(s2, red) / (float)W + eps);
-    float* hr = h + (size_t)row * W;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float v = xr[c] * r2 * norm_scale(wnext, c, plain);
-        hr[c] = v;
-        split_store(hhi, hlo, (size_t)row * W + c, v);
+    for (int c = threadIdx.x * V; c < W; c += step) {
+        float t[V], wn[V];
+        ld_vec<V>(x + rb + c, t); ld_vec<V>(wnext + c, wn);
+#pragma unroll
+        for (int i = 0; i < V; ++i) t[i] = t[i] * r2 * (plain ? wn[i] : 1.f + wn[i]);
+        st_vec<V>(h + rb + c, t);
+        split_store_vec<V>(hhi, hlo, rb + c, t);
     }
 }
 
@@ -919,17 +984,46 @@ static __global__ void ly_conv_state_kernel(ConvArgs a) {
 }
 
 // The input convolution in front of a sublayer: out[row, c] = in[row, c] + sum_k w[c, k] * in[position - (taps - 1 - k), c] (no bias,
-// no activation; a.proj / a.off name `in`), with its hi | lo halves.  grid (rows, channel blocks).
-static __global__ void ly_input_conv_kernel(ConvArgs a, float* __restrict__ out, uint16_t* __restrict__ ohi, uint16_t* __restrict__ olo) {
-    const int row = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+// no activation; a.proj / a.off name `in`), with its hi | lo halves.  grid (row blocks of `rpb` rows, channel blocks); a thread takes V
+// consecutive channels (V = 4: 16-byte accesses; ch, ldp and off multiples of 4) through the block's rows in turn and keeps its
+// channels' taps in its own shared-memory cells ([taps][threads][V] floats: no barrier is needed).
+template <int V>
+static __global__ void __launch_bounds__(128) ly_input_conv_kernel(ConvArgs a, int rpb, int T, float* __restrict__ out, uint16_t* __restrict__ ohi,
+                                                                     uint16_t* __restrict__ olo) {
+    extern __shared__ __align__(16) float wsm[];
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
     if (c >= a.ch) return;
-    const int seq = a.row_seq[row], pos = a.row_pos[row];
-    const int row0 = a.seq_row0[seq], pos0 = a.seq_pos0[seq], slot = a.seq_slot[seq];
-    float t = 0.f;
-    for (int k = 0; k < a.taps; ++k) t = fmaf(a.w[(size_t)c * a.taps + k], conv_input(a, row, row0, pos, pos0, slot, a.taps - 1 - k, c), t);
-    t += a.proj[(size_t)row * a.ldp + a.off + c];
-    out[(size_t)row * a.ch + c] = t;
-    split_store(ohi, olo, (size_t)row * a.ch + c, t);
+    for (int k = 0; k < a.taps; ++k)
+#pragma unroll
+        for (int i = 0; i < V; ++i) wsm[((size_t)k * blockDim.x + threadIdx.x) * V + i] = a.w[(size_t)(c + i) * a.taps + k];
+    const int r_hi = min(T, (int)(blockIdx.x + 1) * rpb);
+    for (int row = blockIdx.x * rpb; row < r_hi; ++row) {
+        const int seq = a.row_seq[row], pos = a.row_pos[row];
+        const int row0 = a.seq_row0[seq], pos0 = a.seq_pos0[seq], slot = a.seq_slot[seq];
+        float t[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) t[i] = 0.f;
+        for (int k = 0; k < a.taps; ++k) {
+            const int back = a.taps - 1 - k;
+            const float* src;
+            if (row - back >= row0) src = a.proj + (size_t)(row - back) * a.ldp + a.off;
+            else {
+                const int p = pos - back;
+                if (p < 0) continue;                 // before the sequence's start: zeros
+                src = a.state + ((size_t)slot * (a.taps - 1) + (p - pos0 + a.taps - 1)) * a.ch;
+            }
+            float in[V], wk[V];
+            ld_vec<V>(src + c, in); ld_vec<V>(wsm + ((size_t)k * blockDim.x + threadIdx.x) * V, wk);
+#pragma unroll
+            for (int i = 0; i < V; ++i) t[i] = fmaf(wk[i], in[i], t[i]);
+        }
+        float self[V];
+        ld_vec<V>(a.proj + (size_t)row * a.ldp + a.off + c, self);
+#pragma unroll
+        for (int i = 0; i < V; ++i) t[i] += self[i];
+        st_vec<V>(out + (size_t)row * a.ch + c, t);
+        split_store_vec<V>(ohi, olo, (size_t)row * a.ch + c, t);
+    }
 }
 
 // Mamba-2, per row: x | B | C <- silu(conv + bias);  per head  b = softplus(dt + dt_bias),  a = exp(-exp(A_log) b)  -> ab[row, h] = (a, b).

@@ -159,12 +159,12 @@ def tc_cfg():
 
 
 def tc_cfg_partial_tiles():
-    """192-wide: three 64-column k blocks, matrices that end inside a 128-row tile; the first layer's experts lie outside the tiles
+    """320-wide: five 64-column k blocks, matrices that end inside a 128-row tile; the first layer's experts lie outside the tiles
     (ff = 100) and run on the plain kernel beside tensor-core projections"""
     return config([layer(left(heads=3, kv_heads=1, dim=48, vdim=64, window=90), right(heads=3, kv_heads=3, dim=64, vdim=64, conv=4),
                          mlp=moe(experts=6, top=2, ff=100, groups=3, keep=2)),
                    layer(left(heads=6, kv_heads=3, dim=32, vdim=24, window=64), right(heads=3, kv_heads=1, dim=24, vdim=40, conv=2),
-                         mlp=moe(experts=6, top=2, ff=192, groups=2, keep=1))], vocab=200, width=192)
+                         mlp=moe(experts=6, top=2, ff=320, groups=2, keep=1))], vocab=200, width=320)
 
 
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
