@@ -389,6 +389,23 @@ def test_long_decoding(dtype):
     assert relerr(run_cut(model, toks, [10]), oracle.run(toks), 0.02 if dtype == "bf16" else 0.0) < TOL[dtype]
 
 
+def test_steps_of_more_than_a_thousand_rows():
+    """long steps take the input convolution through blocks that walk several rows: two requests in one step, the border between
+    them inside a block of rows, then portions that start in the middle of such a block"""
+    cfg = config([layer(left(window=100)), layer(left(heads=2, kv_heads=1, window=7), mlp=None)], width=40, taps=4, max_positions=1200)
+    oracle, model = build(cfg, seed=19)
+    a, b = tokens(cfg, 1100, seed=1), tokens(cfg, 75, seed=2)
+    ra, rb = oracle.run(a), oracle.run(b)
+    cache = model.new_device_cache(max_batch=2, max_seq=1152, pool_tokens=1152 + 128)
+    lg = cache.forward_ragged([1, 0], [b[:3], a[:1027]], [list(range(3)), list(range(1027))])
+    assert relerr(lg[:3], rb[:3]) < TOL["f32"] and relerr(lg[3:], ra[:1027]) < TOL["f32"]
+    lg = cache.forward_ragged([0, 1], [a[1027:], b[3:]], [list(range(73)), list(range(72))])
+    assert relerr(lg[:73], ra[1027:]) < TOL["f32"] and relerr(lg[73:], rb[3:]) < TOL["f32"]
+    cache.slot_reset(0)
+    lg = cache.forward_ragged([0], [a], [list(range(1100))])
+    assert relerr(lg, ra) < TOL["f32"]
+
+
 def test_position_table_bounds_a_sequence():
     cfg = config([layer()], max_positions=70)
     oracle, model = build(cfg, seed=18)
