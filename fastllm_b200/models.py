@@ -727,7 +727,7 @@ class TozaraxWithConfig(_LayeredBase):
 
     @classmethod
     def stack_options(cls, config: dict, sc) -> None:
-        sc.max_positions = int(config["max_positions"])
+        sc.max_positions = int(config.get("max_positions") or 0)
         sc.canon_taps = int((config.get("canon") or {}).get("taps") or 0)
         sc.gated_residual, sc.depth_avg = 1, 1
 
@@ -736,7 +736,7 @@ class TozaraxWithConfig(_LayeredBase):
         return tozarax_layer_descs(config)
 
     def _capacity(self) -> int:
-        return min(self.KV_CAPACITY, int(self.config["max_positions"]))
+        return min(self.KV_CAPACITY, int(self.config.get("max_positions") or self.KV_CAPACITY))
 
 
 # every adapter, in the order the registry tries them (model_registry.rs:169-182 keeps the same kind of list)
