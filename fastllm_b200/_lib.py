@@ -11,9 +11,10 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libfastllm_b200.so")
 
-FL_ARCH = {"llama": 0, "mistral": 1, "qwen2": 2, "mixtral": 3, "bert": 4, "nifunex": 5, "rofetar": 6, "tozarax": 7}
-FL_MIXER = {"gla": 0, "latent_attention": 1, "attention": 2, "mamba2": 3, "delta": 4}
-FL_ACT = {"swish_clamp": 0, "gelu_tanh": 1, "relu2": 2}
+FL_ARCH = {"llama": 0, "mistral": 1, "qwen2": 2, "mixtral": 3, "bert": 4, "nifunex": 5, "rofetar": 6, "tozarax": 7, "medulorn": 8}
+FL_MIXER = {"gla": 0, "latent_attention": 1, "attention": 2, "mamba2": 3, "delta": 4, "lightning": 5}
+FL_ACT = {"swish_clamp": 0, "gelu_tanh": 1, "relu2": 2, "relu": 3}
+FL_ROT_SCALE = {"yarn": 0, "bands": 1}
 FL_ROUTER = {"softmax": 0, "sigmoid_groups": 1}
 FL_FFN = {"none": 0, "dense": 1, "moe": 2}
 FL_DTYPE_F32, FL_DTYPE_BF16, FL_DTYPE_F16 = 0, 1, 2
@@ -38,14 +39,17 @@ class FlLayerDesc(C.Structure):
                 ("kv_heads", C.c_int32), ("conv", C.c_int32), ("state", C.c_int32), ("groups", C.c_int32), ("norm_groups", C.c_int32),
                 ("softcap", C.c_float), ("sink", C.c_int32), ("rot_halves", C.c_int32), ("ffn_act", C.c_int32), ("ffn_bias", C.c_int32),
                 ("no_qk_norm", C.c_int32), ("beside", C.c_int32), ("router", C.c_int32), ("route_groups", C.c_int32),
-                ("route_keep", C.c_int32), ("reserved", C.c_int32 * 1)]
+                ("route_keep", C.c_int32), ("qkv_bias", C.c_int32), ("qk_norm_whole", C.c_int32), ("mask_chunk", C.c_int32),
+                ("keep_first", C.c_int32), ("rot_scaling", C.c_int32), ("out_scale", C.c_float), ("pair_sum", C.c_int32),
+                ("router_bias", C.c_int32), ("shared_plain", C.c_int32), ("reserved", C.c_int32 * 2)]
 
 
 class FlStackConfig(C.Structure):
     _fields_ = [("arch", C.c_int32), ("vocab", C.c_int32), ("width", C.c_int32), ("n_layers", C.c_int32), ("norm_eps", C.c_float),
                 ("compute_dtype", C.c_int32), ("norm_plain", C.c_int32), ("no_pre_norm", C.c_int32), ("no_post_norm", C.c_int32),
                 ("max_positions", C.c_int32), ("canon_taps", C.c_int32), ("gated_residual", C.c_int32), ("depth_avg", C.c_int32),
-                ("reserved", C.c_int32 * 3)]
+                ("post_sum_norm", C.c_int32), ("residual_alpha", C.c_float), ("norm_scalar", C.c_int32), ("embed_scale", C.c_float),
+                ("logit_softcap", C.c_float), ("token_shift", C.c_int32), ("reserved", C.c_int32 * 3)]
 
 
 class FastllmError(RuntimeError):

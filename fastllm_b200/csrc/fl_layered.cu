@@ -1,4 +1,4 @@
-// Layered decoders (FL_ARCH_NIFUNEX, FL_ARCH_ROFETAR, FL_ARCH_TOZARAX): weight layout + ingest, pooled cache (pages of latents or keys | values +
+// Layered decoders (FL_ARCH_NIFUNEX, FL_ARCH_ROFETAR, FL_ARCH_TOZARAX, FL_ARCH_MEDULORN): weight layout + ingest, pooled cache (pages of latents or keys | values +
 // recurrent-state slots), and the step function for mixed batches (portions of prompts beside single decoded tokens).
 #include <cmath>
 #include <map>
@@ -36,7 +36,8 @@ static float half_to_f32(uint16_t h) {
 
 // where a named tensor goes
 struct LyRoute {
-    enum Kind { MAT16, F32, UK_T } kind;
+    enum Kind { MAT16, F32, UK_T, F32_RAW, F32_FILL } kind;     // F32_RAW: f32 input is kept bit for bit (constants of a design, not
+                                                                // weights); F32_FILL: a tensor of ONE element fills rows x cols floats
     void* dst;
     int64_t rows, cols;     // shape handed over
     int heads;              // UK_T: source rows = heads * (rows / heads)
@@ -51,8 +52,8 @@ static void check_mixer(const LayeredModel& m, int i, const fl_layer_desc& d, bo
     const std::string at = "layer " + std::to_string(i) + (second ? " (second mixer): " : ": ");
     FL_CHECK(d.heads >= 1 && (d.dim >= 1 || d.mixer == FL_MIXER_MAMBA2) && d.vdim >= 1, FL_ERR_INVALID, at + "heads / dim / vdim must be positive");
     if (second || d.beside)
-        FL_CHECK((d.mixer == FL_MIXER_ATTN || d.mixer == FL_MIXER_DELTA) && d.kv_from < 0, FL_ERR_UNSUPPORTED,
-                 at + "mixers side by side: attention or delta rule, each with its own cache");
+        FL_CHECK((d.mixer == FL_MIXER_ATTN || d.mixer == FL_MIXER_DELTA || d.mixer == FL_MIXER_LIGHTNING) && d.kv_from < 0, FL_ERR_UNSUPPORTED,
+                 at + "mixers side by side: attention, delta rule or lightning attention, each with its own cache");
     if (d.mixer == FL_MIXER_GLA) {
         FL_CHECK(d.decay_rank >= 1 && d.decay_rank <= 4096 && d.tau > 0.f, FL_ERR_INVALID, at + "bad decay rank / tau");
         FL_CHECK(d.dim <= 256, FL_ERR_UNSUPPORTED, at + "gated linear attention: at most 256 key channels per head");
@@ -75,6 +76,10 @@ static void check_mixer(const LayeredModel& m, int i, const fl_layer_desc& d, bo
         FL_CHECK(d.dim <= 256 && d.vdim <= 256, FL_ERR_UNSUPPORTED, at + "attention: at most 256 channels per head");
         FL_CHECK(d.rot_dims >= 0 && d.rot_dims <= d.dim && d.rot_dims % 2 == 0, FL_ERR_INVALID, at + "rotated channels must be even and <= dim");
         FL_CHECK(d.window >= 0 && d.softcap >= 0.f, FL_ERR_INVALID, at + "negative window / score cap");
+        FL_CHECK(d.keep_first >= 0 && d.mask_chunk >= 0 && d.sink >= 0 && d.sink <= 2, FL_ERR_INVALID, at + "bad mask sizes / sink kind");
+        FL_CHECK(d.rot_scaling == FL_ROT_SCALE_YARN || d.rot_scaling == FL_ROT_SCALE_BANDS, FL_ERR_INVALID, at + "unknown rotary scaling");
+        FL_CHECK(!(d.qk_norm_whole && d.no_qk_norm), FL_ERR_INVALID, at + "a q/k norm over the whole projection needs the q/k norm");
+        FL_CHECK(!(d.qkv_bias && d.kv_from >= 0), FL_ERR_UNSUPPORTED, at + "biased projections are built for layers with their own cache");
         if (d.kv_from >= 0) {
             FL_CHECK(d.kv_from < i, FL_ERR_INVALID, at + "kv_from must name an earlier layer");
             const fl_layer_desc& s = m.layers[d.kv_from].d;
@@ -92,6 +97,8 @@ static void check_mixer(const LayeredModel& m, int i, const fl_layer_desc& d, bo
         FL_CHECK(d.heads % G == 0, FL_ERR_INVALID, at + "heads must be a multiple of kv_heads");
         FL_CHECK(d.dim <= 256, FL_ERR_UNSUPPORTED, at + "delta rule: at most 256 key channels per head");
         FL_CHECK(d.conv >= 1 && d.conv <= kMaxTaps, FL_ERR_UNSUPPORTED, at + "convolution taps must be in 1..16");
+    } else if (d.mixer == FL_MIXER_LIGHTNING) {
+        FL_CHECK(d.dim <= 256, FL_ERR_UNSUPPORTED, at + "lightning attention: at most 256 key channels per head");
     } else {
         FL_CHECK(false, FL_ERR_INVALID, at + "unknown mixer");
     }
@@ -100,8 +107,9 @@ static void check_mixer(const LayeredModel& m, int i, const fl_layer_desc& d, bo
 static void check_layer(const LayeredModel& m, int i, const fl_layer_desc& d) {
     const std::string at = "layer " + std::to_string(i) + ": ";
     check_mixer(m, i, d, false);
-    FL_CHECK(d.ffn_act == FL_ACT_SWISH_CLAMP || d.ffn_act == FL_ACT_GELU_TANH || d.ffn_act == FL_ACT_RELU2, FL_ERR_INVALID,
+    FL_CHECK(d.ffn_act == FL_ACT_SWISH_CLAMP || d.ffn_act == FL_ACT_GELU_TANH || d.ffn_act == FL_ACT_RELU2 || d.ffn_act == FL_ACT_RELU, FL_ERR_INVALID,
              at + "unknown feed-forward activation");
+    FL_CHECK(!(d.ffn_act == FL_ACT_RELU && d.ffn_bias), FL_ERR_UNSUPPORTED, at + "the relu-gated feed-forward has no biases");
     FL_CHECK(d.ffn != FL_FFN_MOE || ((d.ffn_act == FL_ACT_SWISH_CLAMP || d.ffn_act == FL_ACT_RELU2) && !d.ffn_bias), FL_ERR_UNSUPPORTED,
              at + "experts use the clamped or the squared-relu activation, without biases");
     FL_CHECK(!(d.ffn_act == FL_ACT_RELU2 && d.ffn_bias), FL_ERR_UNSUPPORTED, at + "the squared-relu feed-forward has no biases");
@@ -116,6 +124,7 @@ static void check_layer(const LayeredModel& m, int i, const fl_layer_desc& d) {
                      at + "experts must divide into route_groups groups of which 1..route_groups are kept");
             FL_CHECK(d.top <= d.route_keep * (d.experts / d.route_groups), FL_ERR_INVALID, at + "the kept groups hold fewer than `top` experts");
             FL_CHECK(d.shared_ff == 0, FL_ERR_UNSUPPORTED, at + "the sigmoid router has no shared expert");
+            FL_CHECK(!d.router_bias, FL_ERR_UNSUPPORTED, at + "the sigmoid router has a choice correction, not a bias");
         }
     } else {
         FL_CHECK(d.ffn == FL_FFN_NONE, FL_ERR_INVALID, at + "unknown feed-forward kind");
@@ -124,13 +133,19 @@ static void check_layer(const LayeredModel& m, int i, const fl_layer_desc& d) {
 
 void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
     const fl_stack_config& c = m.cfg;
-    FL_CHECK(c.arch == FL_ARCH_NIFUNEX || c.arch == FL_ARCH_ROFETAR || c.arch == FL_ARCH_TOZARAX, FL_ERR_INVALID, "layered models: unknown arch");
+    FL_CHECK(c.arch == FL_ARCH_NIFUNEX || c.arch == FL_ARCH_ROFETAR || c.arch == FL_ARCH_TOZARAX || c.arch == FL_ARCH_MEDULORN, FL_ERR_INVALID,
+             "layered models: unknown arch");
     FL_CHECK(c.vocab >= 1 && c.width >= 1 && c.n_layers >= 1 && c.n_layers <= 4096, FL_ERR_INVALID, "layered models: sizes must be positive");
     FL_CHECK(c.compute_dtype == FL_DTYPE_BF16 || c.compute_dtype == FL_DTYPE_F32, FL_ERR_INVALID, "compute_dtype must be bf16 or f32");
     FL_CHECK(!(c.no_pre_norm && c.no_post_norm), FL_ERR_INVALID, "a stack norms its sublayers' inputs, their outputs, or both");
     FL_CHECK(c.max_positions >= 0 && c.canon_taps >= 0 && c.canon_taps <= kMaxTaps, FL_ERR_INVALID, "bad position table / input convolution size");
     FL_CHECK(c.no_post_norm || !(c.gated_residual || c.depth_avg), FL_ERR_UNSUPPORTED,
              "gated contributions and the depth average are built for stacks whose sublayer results join the stream un-normed");
+    FL_CHECK(!c.post_sum_norm || (c.no_pre_norm && !c.no_post_norm && c.norm_plain), FL_ERR_INVALID,
+             "a norm of the sum is built for stacks whose sublayers read the stream itself, with plain norm weights");
+    FL_CHECK(!(c.token_shift && c.canon_taps > 0), FL_ERR_UNSUPPORTED, "a stack has a token shift or input convolutions, not both");
+    FL_CHECK(!c.token_shift || c.no_pre_norm, FL_ERR_UNSUPPORTED, "the token shift is built for stacks whose mixers read the stream itself");
+    FL_CHECK(c.logit_softcap >= 0.f, FL_ERR_INVALID, "negative logit cap");
     m.W = c.width; m.V = c.vocab; m.L = c.n_layers; m.f32 = c.compute_dtype == FL_DTYPE_F32;
     m.layers.resize(m.L);
     struct Reg { void** pp; size_t bytes; };
@@ -150,7 +165,7 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             m.max_heads = std::max<int>(m.max_heads, (int)H);
         };
         auto rope = [&]() {
-            const RopeSpec rs{d.rot_dims, d.rot_base, d.yarn_factor, d.yarn_original, d.yarn_fast, d.yarn_slow};
+            const RopeSpec rs{d.rot_dims, d.rot_base, d.yarn_factor, d.yarn_original, d.yarn_fast, d.yarn_slow, d.rot_scaling};
             int ri = -1;
             for (size_t k = 0; k < m.ropes.size(); ++k)
                 if (m.ropes[k] == rs) ri = (int)k;
@@ -161,11 +176,13 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             if (lw.d.kv_heads <= 0) lw.d.kv_heads = lw.d.heads;
             const size_t G = lw.d.kv_heads;
             lw.off_q = 0; lw.n_in = (int)(H * D); lw.off_k = lw.off_v = -1;
-            if (!d.no_qk_norm) reg(&lw.qnorm, D * 4);
+            if (!d.no_qk_norm) reg(&lw.qnorm, (d.qk_norm_whole ? H * D : D) * 4);
+            if (d.qkv_bias) { reg(&lw.bq, H * D * 4); reg(&lw.bk, G * D * 4); reg(&lw.bv, G * Dv * 4); }
+            if (d.sink == 2) reg(&lw.sinkv, H * 4);
             m.max_av = std::max<int>(m.max_av, (int)Dv);
             if (d.kv_from < 0) {
                 lw.off_k = lw.n_in; lw.off_v = lw.off_k + (int)(G * D); lw.n_in = lw.off_v + (int)(G * Dv);
-                if (!d.no_qk_norm) reg(&lw.knorm, D * 4);
+                if (!d.no_qk_norm) reg(&lw.knorm, (d.qk_norm_whole ? G * D : D) * 4);
                 lw.kv_owner = i;
                 lw.kv_index = (int)m.kv_layers.size();
                 m.kv_layers.push_back(&lw);
@@ -194,6 +211,12 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             lw.conv_off = 0; lw.conv_ch = lw.off_g;
             reg(&lw.conv_w, (size_t)lw.conv_ch * d.conv * 4);
             reg(&lw.a_log, H * 4); reg(&lw.dt_bias, H * 4); reg(&lw.hnorm, Dv * 4);
+            recurrent();
+        } else if (d.mixer == FL_MIXER_LIGHTNING) {
+            lw.off_q = 0; lw.off_k = (int)(H * D); lw.off_v = (int)(2 * H * D); lw.off_g = lw.off_v + (int)(H * Dv);
+            lw.n_in = pad8(lw.off_g + (int)(H * Dv));
+            lw.conv_off = 0; lw.conv_ch = lw.off_g;         // the activated span q | k | v (no convolution: conv = 0 taps)
+            reg(&lw.decay, H * 4); reg(&lw.hnorm, H * Dv * 4);
             recurrent();
         } else if (d.mixer == FL_MIXER_GLA) {
             lw.off_q = 0; lw.off_k = (int)(H * D); lw.off_v = (int)(2 * H * D); lw.off_g = lw.off_v + (int)(H * Dv);
@@ -239,9 +262,11 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
         const bool pre = !c.no_pre_norm, post = !c.no_post_norm;
         if (pre) reg(&lw.norm1, W * 4);
         if (post) reg(&lw.norm1b, W * 4);
+        if (c.token_shift) reg(&lw.shift, W * 4);
         build_mixer(lw, i, 0);
         if (d.beside) {
-            FL_CHECK(!post, FL_ERR_UNSUPPORTED, "mixers side by side are built for stacks whose sublayer results join the stream un-normed");
+            FL_CHECK(d.pair_sum ? c.post_sum_norm != 0 : !post, FL_ERR_UNSUPPORTED,
+                     "mixers side by side: their normed mean joins the stream un-normed, or their weighted sum enters a norm of the sum");
             lw.side = std::make_shared<LayeredLayerW>();
             lw.side->d = descs[next_desc++];
             lw.side->d.beside = 0;
@@ -249,7 +274,7 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             build_mixer(*lw.side, i, lw.n_in);
             lw.n_in += lw.side->n_in;
             lw.side->n_in = lw.n_in;                    // both read rows of the same projected buffer
-            reg(&lw.pair_wa, W * 4); reg(&lw.pair_wb, W * 4);
+            if (!d.pair_sum) { reg(&lw.pair_wa, W * 4); reg(&lw.pair_wb, W * 4); }
         }
         reg(&lw.w_in, (size_t)lw.n_in * W * 2);
         m.max_in = std::max(m.max_in, lw.n_in);
@@ -268,11 +293,12 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             m.max_top = std::max(m.max_top, d.ffn == FL_FFN_MOE ? d.top : 1);
             if (d.ffn == FL_FFN_MOE) {
                 reg(&lw.router, (size_t)d.experts * W * 4);
+                if (d.router_bias) reg(&lw.router_b, (size_t)d.experts * 4);
                 if (d.router == FL_ROUTER_SIGMOID_GROUPS) reg(&lw.route_corr, (size_t)d.experts * 4);
                 m.max_experts = std::max(m.max_experts, d.experts);
                 if (d.shared_ff > 0) {
                     reg(&lw.s_gu, (size_t)2 * d.shared_ff * W * 2); reg(&lw.s_down, W * (size_t)d.shared_ff * 2);
-                    reg(&lw.shared_gate, W * 4);
+                    if (!d.shared_plain) reg(&lw.shared_gate, W * 4);
                     m.max_ff = std::max(m.max_ff, d.shared_ff);
                 }
             }
@@ -291,7 +317,9 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
         R.r[n] = LyRoute{LyRoute::MAT16, base + row0 * cols, rows, cols, 0};
     };
     auto vec = [&](const std::string& n, float* base, int64_t rows, int64_t cols) { R.r[n] = LyRoute{LyRoute::F32, base, rows, cols, 0}; };
-    mat("embed", m.embed, 0, m.V, W); mat("head", m.head, 0, m.V, W); vec("final.norm", m.final_norm, W, 1);
+    // a layer norm's weight: [W], or one number for all channels (norm_scalar), kept as W equal floats so that the kernels index it alike
+    auto normw = [&](const std::string& n, float* base) { R.r[n] = LyRoute{c.norm_scalar ? LyRoute::F32_FILL : LyRoute::F32, base, (int64_t)W, 1, 0}; };
+    mat("embed", m.embed, 0, m.V, W); mat("head", m.head, 0, m.V, W); normw("final.norm", m.final_norm);
     if (m.pos != nullptr) mat("pos", m.pos, 0, c.max_positions, W);
     // the tensors of one mixer, named p + "q" and so on (p = "l<i>.mix." or "l<i>.mix.left." / "l<i>.mix.right.")
     auto route_mixer = [&](const LayeredLayerW& lw, const std::string& p) {
@@ -300,11 +328,13 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
         if (d.mixer == FL_MIXER_ATTN) {
             const int64_t G = d.kv_heads;
             mat(p + "q", lw.w_in, lw.off_q, H * D, W);
-            if (!d.no_qk_norm) vec(p + "q.norm", lw.qnorm, D, 1);
+            if (!d.no_qk_norm) vec(p + "q.norm", lw.qnorm, d.qk_norm_whole ? H * D : D, 1);
             if (d.kv_from < 0) {
                 mat(p + "k", lw.w_in, lw.off_k, G * D, W); mat(p + "v", lw.w_in, lw.off_v, G * Dv, W);
-                if (!d.no_qk_norm) vec(p + "k.norm", lw.knorm, D, 1);
+                if (!d.no_qk_norm) vec(p + "k.norm", lw.knorm, d.qk_norm_whole ? G * D : D, 1);
             }
+            if (d.qkv_bias) { vec(p + "q.b", lw.bq, H * D, 1); vec(p + "k.b", lw.bk, G * D, 1); vec(p + "v.b", lw.bv, G * Dv, 1); }
+            if (d.sink == 2) vec(p + "sink", lw.sinkv, H, 1);
         } else if (d.mixer == FL_MIXER_MAMBA2) {
             mat(p + "in", lw.w_in, lw.off_g, lw.off_dt - lw.off_g + H, W);
             vec(p + "conv", lw.conv_w, lw.conv_ch, d.conv); vec(p + "conv.b", lw.conv_b, lw.conv_ch, 1);
@@ -319,6 +349,11 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             vec(p + "k.conv", lw.conv_w + (size_t)(lw.off_k - lw.conv_off) * d.conv, G * D, d.conv);
             vec(p + "v.conv", lw.conv_w + (size_t)(lw.off_v - lw.conv_off) * d.conv, H * Dv, d.conv);
             vec(p + "A_log", lw.a_log, H, 1); vec(p + "dt_bias", lw.dt_bias, H, 1); vec(p + "norm", lw.hnorm, Dv, 1);
+        } else if (d.mixer == FL_MIXER_LIGHTNING) {
+            mat(p + "q", lw.w_in, lw.off_q, H * D, W); mat(p + "k", lw.w_in, lw.off_k, H * D, W);
+            mat(p + "v", lw.w_in, lw.off_v, H * Dv, W); mat(p + "g", lw.w_in, lw.off_g, H * Dv, W);
+            vec(p + "norm", lw.hnorm, H * Dv, 1);
+            R.r[p + "decay"] = LyRoute{LyRoute::F32_RAW, lw.decay, H, 1, 0};
         } else if (d.mixer == FL_MIXER_GLA) {
             mat(p + "q", lw.w_in, lw.off_q, H * D, W); mat(p + "k", lw.w_in, lw.off_k, H * D, W);
             mat(p + "v", lw.w_in, lw.off_v, H * Dv, W); mat(p + "g", lw.w_in, lw.off_g, H * Dv, W);
@@ -338,12 +373,13 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
         const fl_layer_desc& d = lw.d;
         const std::string p = "l" + std::to_string(i) + ".";
         const bool pre = !c.no_pre_norm, post = !c.no_post_norm;
-        if (pre && post) { vec(p + "norm1", lw.norm1, W, 1); vec(p + "norm1b", lw.norm1b, W, 1); }
-        else vec(p + "norm1", pre ? lw.norm1 : lw.norm1b, W, 1);
+        if (pre && post) { normw(p + "norm1", lw.norm1); normw(p + "norm1b", lw.norm1b); }
+        else normw(p + "norm1", pre ? lw.norm1 : lw.norm1b);
+        if (lw.shift) vec(p + "shift", lw.shift, W, 1);
         if (lw.side) {
             lw.side->w_in = lw.w_in;
             route_mixer(lw, p + "mix.left."); route_mixer(*lw.side, p + "mix.right.");
-            vec(p + "mix.left.out", lw.pair_wa, W, 1); vec(p + "mix.right.out", lw.pair_wb, W, 1);
+            if (lw.pair_wa) { vec(p + "mix.left.out", lw.pair_wa, W, 1); vec(p + "mix.right.out", lw.pair_wb, W, 1); }
         } else {
             route_mixer(lw, p + "mix.");
         }
@@ -351,8 +387,8 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
         if (lw.rg1) { mat(p + "rg1", lw.rg1, 0, W, W); vec(p + "rg1.b", lw.rg1b, W, 1); }
         if (lw.dwa) vec(p + "dwa", lw.dwa, i + 2, 1);
         if (d.ffn == FL_FFN_NONE) continue;
-        if (pre && post) { vec(p + "norm2", lw.norm2, W, 1); vec(p + "norm2b", lw.norm2b, W, 1); }
-        else vec(p + "norm2", pre ? lw.norm2 : lw.norm2b, W, 1);
+        if (pre && post) { normw(p + "norm2", lw.norm2); normw(p + "norm2b", lw.norm2b); }
+        else normw(p + "norm2", pre ? lw.norm2 : lw.norm2b);
         if (lw.canon2) vec(p + "canon2", lw.canon2, W, c.canon_taps);
         if (lw.rg2) { mat(p + "rg2", lw.rg2, 0, W, W); vec(p + "rg2.b", lw.rg2b, W, 1); }
         const int64_t F = d.ff;
@@ -366,6 +402,7 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             }
         } else {
             vec(p + "mlp.router", lw.router, d.experts, W);
+            if (lw.router_b) vec(p + "mlp.router.b", lw.router_b, d.experts, 1);
             if (lw.route_corr) vec(p + "mlp.correction", lw.route_corr, d.experts, 1);
             for (int e = 0; e < d.experts; ++e) {
                 const std::string q = p + "mlp.e" + std::to_string(e) + ".";
@@ -376,7 +413,8 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             if (d.shared_ff > 0) {
                 const int64_t Fs = d.shared_ff;
                 mat(p + "mlp.shared.gate", lw.s_gu, 0, Fs, W); mat(p + "mlp.shared.up", lw.s_gu, Fs, Fs, W);
-                mat(p + "mlp.shared.down", lw.s_down, 0, W, Fs); vec(p + "mlp.shared.sg", lw.shared_gate, 1, W);
+                mat(p + "mlp.shared.down", lw.s_down, 0, W, Fs);
+                if (lw.shared_gate) vec(p + "mlp.shared.sg", lw.shared_gate, 1, W);
             }
         }
     }
@@ -399,19 +437,29 @@ void layered_put_tensor(LayeredModel& m, const char* name, int dtype, const int6
     if (r == nullptr) { m.ignored++; return; }       // a tensor the layers do not read
     int64_t numel = 1;
     for (int i = 0; i < rank; ++i) numel *= shape[i];
-    const bool shape_ok = numel == r->rows * r->cols && (rank == 1 || (rank == 2 && (shape[0] == r->rows || r->cols == 1 || r->rows == 1)));
+    const bool shape_ok = r->kind == LyRoute::F32_FILL
+                              ? numel == 1
+                              : numel == r->rows * r->cols && (rank == 1 || (rank == 2 && (shape[0] == r->rows || r->cols == 1 || r->rows == 1)));
     FL_CHECK(shape_ok, FL_ERR_INVALID, std::string("shape mismatch for ") + name);
     FL_CHECK(dtype == FL_DTYPE_F32 || dtype == FL_DTYPE_BF16 || dtype == FL_DTYPE_F16, FL_ERR_INVALID, "bad dtype");
+    if (r->kind == LyRoute::F32_RAW && dtype == FL_DTYPE_F32) {
+        FL_CUDA(cudaMemcpy(r->dst, host, (size_t)numel * 4, cudaMemcpyHostToDevice));
+        m.have.insert(name);
+        return;
+    }
     std::vector<uint16_t> bits((size_t)numel);
     if (dtype == FL_DTYPE_BF16) std::memcpy(bits.data(), host, (size_t)numel * 2);
     else if (dtype == FL_DTYPE_F32) for (int64_t i = 0; i < numel; ++i) bits[i] = f32_to_bits(((const float*)host)[i]);
     else for (int64_t i = 0; i < numel; ++i) bits[i] = f32_to_bits(half_to_f32(((const uint16_t*)host)[i]));
     if (r->kind == LyRoute::MAT16) {
         FL_CUDA(cudaMemcpy(r->dst, bits.data(), (size_t)numel * 2, cudaMemcpyHostToDevice));
-    } else if (r->kind == LyRoute::F32) {
+    } else if (r->kind == LyRoute::F32 || r->kind == LyRoute::F32_RAW) {
         std::vector<float> v((size_t)numel);
         for (int64_t i = 0; i < numel; ++i) v[i] = bits_to_f32(bits[i]);
         FL_CUDA(cudaMemcpy(r->dst, v.data(), (size_t)numel * 4, cudaMemcpyHostToDevice));
+    } else if (r->kind == LyRoute::F32_FILL) {
+        std::vector<float> v((size_t)(r->rows * r->cols), bits_to_f32(bits[0]));
+        FL_CUDA(cudaMemcpy(r->dst, v.data(), v.size() * 4, cudaMemcpyHostToDevice));
     } else {        // [heads * D, C] -> [heads][C][D]
         const int64_t Hh = r->heads, D = r->rows / Hh, C = r->cols;
         std::vector<uint16_t> t((size_t)numel);
@@ -430,15 +478,17 @@ void layered_random_init(LayeredModel& m, uint64_t seed, float stdv) {
         const LyRoute* r = find_route(m, n);
         const uint64_t ts = tensor_seed(seed, n.c_str());
         const int64_t numel = r->rows * r->cols;
-        if (r->kind == LyRoute::F32) {
+        if (r->kind == LyRoute::F32 || r->kind == LyRoute::F32_RAW || r->kind == LyRoute::F32_FILL) {
             auto ends = [&](const char* t) { const size_t k = std::strlen(t); return n.size() >= k && n.compare(n.size() - k, k, t) == 0; };
             // a plain norm weight sits around one, a zero-centred one around zero
-            const bool around_one = ends("mix.norm") || ends("dkv.norm") || ends("q.norm") || ends("k.norm") || ends("mix.D") || ends("left.out") || ends("right.out") ||
+            const bool around_one = ends("mix.norm") || ends("left.norm") || ends("right.norm") || ends("dkv.norm") || ends("q.norm") || ends("k.norm") || ends("mix.D") || ends("left.out") || ends("right.out") ||
                                     (m.cfg.norm_plain && (ends("norm1") || ends("norm2") || ends("norm1b") || ends("norm2b") || n == "final.norm"));
             const bool is_mat = n.find("router") != std::string::npos || n.find("mix.a2") != std::string::npos || n.find("shared.sg") != std::string::npos ||
                                 ends(".conv") || ends(".canon1") || ends(".canon2");
             const bool is_bias = n.size() >= 4 && n.compare(n.size() - 4, 4, "a2.b") == 0;
             if (around_one) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 1.0f);
+            else if (ends(".decay")) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 0.96875f);
+            else if (ends(".shift")) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 0.25f);
             else if (ends(".dwa")) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 1.0f / (float)numel);     // a plain mean over the outputs so far
             else if (is_bias) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 3.0f);
             else if (is_mat) synth_fill_f32_kernel<<<kNumSMs, 256>>>((float*)r->dst, numel, ts, stdv, ident);
@@ -500,7 +550,18 @@ static void rope_tables(const RopeSpec& rs, int max_seq, std::vector<float>& cs,
     std::vector<double> f(half);
     double mult = 1.0;
     for (int i = 0; i < half; ++i) f[i] = std::pow(rs.base, -2.0 * i / (double)rs.dims);
-    if (rs.yarn_factor > 0.f) {
+    if (rs.yarn_factor > 0.f && rs.scaling == FL_ROT_SCALE_BANDS) {
+        // bands of wavelength: short ones (below original / fast) keep their frequency, long ones (above original / slow) are slowed
+        // by the factor, between the two a linear blend in original / wavelength; magnitude 1
+        const double factor = rs.yarn_factor, orig = rs.yarn_original, hi = rs.yarn_fast, lo = rs.yarn_slow;
+        for (int i = 0; i < half; ++i) {
+            const double wl = 2.0 * M_PI / f[i];
+            if (wl < orig / hi) continue;
+            if (wl > orig / lo) { f[i] /= factor; continue; }
+            const double sm = (orig / wl - lo) / (hi - lo);
+            f[i] = (1.0 - sm) * f[i] / factor + sm * f[i];
+        }
+    } else if (rs.yarn_factor > 0.f) {
         // YaRN: pairs that complete many turns inside the original context keep their frequency, slow pairs are stretched by the
         // factor, a linear ramp between the two pair indices; cos and sin grow by 0.1 ln(factor) + 1
         const double factor = rs.yarn_factor, orig = rs.yarn_original;
@@ -553,6 +614,10 @@ void layered_cache_create(fl_cache& c, int max_slots, int max_seq, int pool_toke
         y.canon_state.resize(m.L);
         for (int i = 0; i < m.L; ++i) y.canon_state[i].alloc((size_t)2 * max_slots * (m.cfg.canon_taps - 1) * m.W, true);
     }
+    if (m.cfg.token_shift) {
+        y.shift_state.resize(m.L);
+        for (int i = 0; i < m.L; ++i) y.shift_state[i].alloc((size_t)max_slots * m.W, true);
+    }
     y.rope_cos.resize(m.ropes.size()); y.rope_sin.resize(m.ropes.size());
     for (size_t k = 0; k < m.ropes.size(); ++k) {
         std::vector<float> cs, sn;
@@ -596,7 +661,7 @@ static void ensure_ws(fl_cache& c, size_t T, size_t n_want) {
         y.proj.alloc(R * m.max_in); y.u.alloc(R * std::max(m.max_hv, 1)); y.go.alloc(R * std::max(m.max_hv, 1));
         y.la.alloc(R * std::max(m.max_hd, 1));
         y.cv.alloc(R * std::max(m.max_cv, 1)); y.rs.alloc(R * 2 * std::max(m.max_heads, 1));
-        if (m.cfg.canon_taps > 0) y.hc.alloc(R * W);
+        if (m.cfg.canon_taps > 0 || m.cfg.token_shift) y.hc.alloc(R * W);
         if (m.cfg.gated_residual) y.gz.alloc(R * W);
         if (m.cfg.depth_avg) y.xs.alloc((size_t)(m.L + 1) * R * W);
         for (const LayeredLayerW& lw : m.layers)
@@ -729,7 +794,7 @@ static void launch_gqa_attn(LaunchCtx& lc, const GqaAttnArgs& a, int T, int max_
     else launch_gqa_attn_rb<CT, 1>(lc, a, T, splits);
     if (splits > 1)
         launch(lc, "gqa_merge", 0, ly_gqa_merge_kernel, dim3(T, a.H), dim3(std::min(256, std::max(32, (a.Dv + 31) / 32 * 32))), 0, (const float*)a.part, splits,
-               a.H, a.Dv, a.sink, a.row_base, a.out, a.ohi, a.olo);
+               a.H, a.Dv, a.sink, a.sinkv, a.row_base, a.out, a.ohi, a.olo);
 }
 
 template <bool DELTA>
@@ -786,8 +851,8 @@ static void latent_attn_tc(fl_cache& c, LaunchCtx& lc, const LayeredLayerW& lw, 
         const CUtensorMap tk = make_tmap_bf16(y.at_kc.p, (uint64_t)nkp, (uint64_t)Ep, (uint64_t)Ep, 128);
         dense_gemm(c, lc, "gemm_tc_attn_scores", rows, nkp, Ep, tk, y.at_s.p, y.at_qhi.p, y.at_qlo.p);
         const int keep = std::min(nkp, kSoftmaxKeep);
-        launch(lc, "attn_softmax", 0, ly_attn_softmax_kernel, dim3(rows), dim3(256), (size_t)keep * 4, (const float*)y.at_s.p, a.row_pos, r0 + f, H, k_lo, nk, nkp,
-               a.window, 0.f, 0, keep, y.at_phi.p, y.at_plo.p);
+        launch(lc, "attn_softmax", 0, ly_attn_softmax_kernel, dim3(rows), dim3(256), (size_t)keep * 4, (const float*)y.at_s.p, a.row_pos, r0 + f, H, k_lo, 0, nk, nkp,
+               a.window, 0, 0, 0.f, 0, (const float*)nullptr, keep, y.at_phi.p, y.at_plo.p);
         const CUtensorMap tv = make_tmap_bf16(y.at_kct.p, (uint64_t)C, (uint64_t)nkp, (uint64_t)nkp, 128);
         dense_gemm(c, lc, "gemm_tc_attn_values", rows, C, nkp, tv, a.ol + (size_t)(r0 + f) * H * C, y.at_phi.p, y.at_plo.p);
     }
@@ -800,10 +865,17 @@ static void gqa_attn_tc(fl_cache& c, LaunchCtx& lc, const GqaAttnArgs& a, int r0
     LayeredCache& y = *c.ly;
     const int H = a.H, G = a.G, rep = H / G, D = a.D, Dv = a.Dv, Dp = (D + 63) / 64 * 64, E = G * (D + Dv);
     const size_t budget = (size_t)48 << 20;                // floats in a score block (192 MB); P halves take the same again
+    // first key of the contiguous range a position reads (window and chunk starts only grow with the position, so a block of
+    // rows needs the keys from its first row's start on), and the kept first keys that lie before it
+    auto start_of = [&](int p) {
+        const int lo_w = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0, lo_c = a.chunk > 0 ? p / a.chunk * a.chunk : 0;
+        return std::max(lo_w, lo_c);
+    };
+    auto first_of = [&](int k_lo) { return a.window > 0 ? std::min(a.keep_first, k_lo) : 0; };
     auto keys_for = [&](int qb, int first) {
         const int p_lo = pos0 + first, p_hi = pos0 + std::min(Ts, first + qb);
-        const int k_lo = (a.window > 0 && p_lo - a.window + 1 > 0) ? p_lo - a.window + 1 : 0;
-        return ((p_hi - k_lo) + 63) / 64 * 64;
+        const int k_lo = start_of(p_lo);
+        return ((p_hi - k_lo) + first_of(k_lo) + 63) / 64 * 64;
     };
     int qb = 1024;
     while (qb > 8 && (size_t)qb * rep * keys_for(qb, std::max(0, Ts - qb)) > budget) qb /= 2;
@@ -818,7 +890,7 @@ static void gqa_attn_tc(fl_cache& c, LaunchCtx& lc, const GqaAttnArgs& a, int r0
     const int* page_row = y.page_table.p + (size_t)slot * c.pages_per_seq;
     for (int f = 0; f < Ts; f += qb) {
         const int nq = std::min(qb, Ts - f), p_lo = pos0 + f, p_hi = p_lo + nq;
-        const int k_lo = (a.window > 0 && p_lo - a.window + 1 > 0) ? p_lo - a.window + 1 : 0, nk = p_hi - k_lo, nkp = (nk + 63) / 64 * 64;
+        const int k_lo = start_of(p_lo), n_first = first_of(k_lo), nk = p_hi - k_lo, nkp = (n_first + nk + 63) / 64 * 64;
         const int rows = nq * rep;
         if (rows <= 128) {          // a short tail: the per-(row, head) kernel
             GqaAttnArgs t = a;
@@ -827,15 +899,15 @@ static void gqa_attn_tc(fl_cache& c, LaunchCtx& lc, const GqaAttnArgs& a, int r0
             continue;
         }
         for (int g = 0; g < G; ++g) {
-            launch(lc, "gqa_gather_kv", 0, ly_gqa_gather_kv_kernel, dim3(nkp), dim3(128), 0, (const uint16_t*)a.pool, page_row, k_lo, nk, nkp, E, g * D, D, Dp,
-                   G * D + g * Dv, Dv, y.at_kc.p, y.at_kct.p);
+            launch(lc, "gqa_gather_kv", 0, ly_gqa_gather_kv_kernel, dim3(nkp), dim3(128), 0, (const uint16_t*)a.pool, page_row, k_lo, n_first, nk, nkp, E, g * D, D,
+                   Dp, G * D + g * Dv, Dv, y.at_kc.p, y.at_kct.p);
             launch(lc, "gqa_build_q", 0, ly_gqa_build_q_kernel, dim3(nq, rep), dim3(128), 0, a.proj, a.ldp, a.off_q, r0 + f, rep, g, D, Dp, a.scale, y.at_qhi.p,
                    y.at_qlo.p);
             const CUtensorMap tk = make_tmap_bf16(y.at_kc.p, (uint64_t)nkp, (uint64_t)Dp, (uint64_t)Dp, 128);
             dense_gemm(c, lc, "gemm_tc_attn_scores", rows, nkp, Dp, tk, y.at_s.p, y.at_qhi.p, y.at_qlo.p);
             const int keep = std::min(nkp, kSoftmaxKeep);
-            launch(lc, "attn_softmax", 0, ly_attn_softmax_kernel, dim3(rows), dim3(256), (size_t)keep * 4, (const float*)y.at_s.p, a.row_pos, r0 + f, rep, k_lo, nk, nkp,
-                   a.window, a.softcap, a.sink, keep, y.at_phi.p, y.at_plo.p);
+            launch(lc, "attn_softmax", 0, ly_attn_softmax_kernel, dim3(rows), dim3(256), (size_t)keep * 4, (const float*)y.at_s.p, a.row_pos, r0 + f, rep, k_lo, n_first,
+                   nk, nkp, a.window, a.keep_first, a.chunk, a.softcap, a.sink, a.sinkv ? a.sinkv + g * rep : (const float*)nullptr, keep, y.at_phi.p, y.at_plo.p);
             const CUtensorMap tv = make_tmap_bf16(y.at_kct.p, (uint64_t)Dv, (uint64_t)nkp, (uint64_t)nkp, 128);
             dense_gemm(c, lc, "gemm_tc_attn_values", rows, Dv, nkp, tv, y.at_o.p + (size_t)g * rows * Dv, y.at_phi.p, y.at_plo.p);
         }
@@ -961,26 +1033,30 @@ static void run_mixer(fl_cache& c, LaunchCtx& lc, const StepTab& st, const Layer
         const int G = d.kv_heads;
         AttnPrepArgs pa{y.proj.p, lw.n_in, lw.off_q, lw.off_k, lw.off_v, lw.qnorm, lw.knorm, eps, y.kv_pool[lw.kv_index], y.page_table.p,
                         c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot, y.rope_cos[lw.rope_index].p, y.rope_sin[lw.rope_index].p,
-                        H, G, D, Dv, d.rot_dims, d.rot_halves};
+                        H, G, D, Dv, d.rot_dims, d.rot_halves, lw.bq, lw.bk, lw.bv, d.qk_norm_whole};
         const size_t psm = (size_t)4 * D * 4;
         if (m.f32) launch(lc, "attn_prep", 0, ly_attn_prep_kernel<float>, dim3(Ti), dim3(128), psm, pa);
         else launch(lc, "attn_prep", 0, ly_attn_prep_kernel<uint16_t>, dim3(Ti), dim3(128), psm, pa);
         GqaAttnArgs at{y.proj.p, lw.n_in, lw.off_q, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot,
-                       y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo, H, G, D, Dv, d.window, d.scale, d.softcap, d.sink, 0, y.at_part.p};
+                       y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo, H, G, D, Dv, d.window, d.scale, d.softcap, d.sink, 0, y.at_part.p,
+                       d.keep_first, d.mask_chunk, lw.sinkv};
         // a step of single tokens is replayed from a captured graph whatever the contexts' lengths: its split count must not follow them
         int max_keys = c.max_seq;
         if (Ti != n) {
             max_keys = 1;
             for (int si = 0; si < n; ++si) max_keys = std::max(max_keys, h_pos0[si] + counts[si]);
         }
-        if (d.window > 0) max_keys = std::min(max_keys, d.window);
+        if (d.window > 0) max_keys = std::min(max_keys, d.window + d.keep_first);
+        if (d.mask_chunk > 0) max_keys = std::min(max_keys, d.mask_chunk);
+        // masks that leave a row few keys: the per-row kernel reads just those, the GEMM path would compute a block's whole rectangle
+        const bool few_keys = (d.window > 0 && d.window + d.keep_first <= 256) || (d.mask_chunk > 0 && d.mask_chunk <= 256);
         // long portions (serving precision): scores and weighted sums as tensor-core GEMMs; decoded tokens, short portions and
         // the exact mode on the per-(row, head) kernel.  Rows are taken in order.
         static const bool tc_attn_off = env_flag("FL_LAYERED_NO_TC_ATTN");
         int done = 0;
         for (int si = 0; si < n; ++si) {
             const int r0 = h_row0[si], Ts = counts[si];
-            if (m.f32 || tc_attn_off || Dv % 8 != 0 || Ts < 64 || (long long)Ts * (H / G) <= 128) continue;
+            if (m.f32 || tc_attn_off || few_keys || Dv % 8 != 0 || Ts < 64 || (long long)Ts * (H / G) <= 128) continue;
             if (r0 > done) {
                 at.row_base = done;
                 launch_gqa_attn<uint16_t>(lc, at, r0 - done, max_keys, true);
@@ -1019,9 +1095,19 @@ static void run_mixer(fl_cache& c, LaunchCtx& lc, const StepTab& st, const Layer
             launch_rec_scan<false>(lc, ra, n);
             const int inner = H * Dv, part = inner / d.norm_groups;
             launch(lc, "gated_group_norm", 0, ly_gated_group_norm_kernel, dim3(Ti, d.norm_groups), dim3(std::min(1024, std::max(64, (part + 31) / 32 * 32))), 0,
-                   (const float*)y.go.p, (const float*)y.proj.p, lw.n_in, lw.off_g, (const float*)lw.hnorm, eps, inner, d.norm_groups, y.u.p,
+                   (const float*)y.go.p, (const float*)y.proj.p, lw.n_in, lw.off_g, (const float*)lw.hnorm, eps, inner, d.norm_groups, 0, y.u.p,
                    lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
         }
+    } else if (d.mixer == FL_MIXER_LIGHTNING) {
+        const int chunk = 512, nchunk = (lw.conv_ch + chunk - 1) / chunk, inner = H * Dv;
+        launch(lc, "lightning_prep", 0, ly_lightning_prep_kernel, dim3(Ti, nchunk), dim3(256), 0, (const float*)y.proj.p, lw.n_in, lw.conv_off, lw.conv_ch, chunk,
+               (const float*)lw.decay, H, y.cv.p, y.rs.p);
+        RecArgs ra{y.cv.p, lw.conv_ch, lw.off_q - lw.conv_off, lw.off_k - lw.conv_off, lw.off_v - lw.conv_off, y.rs.p, (const float*)nullptr, y.go.p,
+                   y.gla_state[lw.gla_index].p, st.seq_row0, st.seq_slot, st.seq_pos0, H, H, D, Dv};
+        launch_rec_scan<false>(lc, ra, n);
+        launch(lc, "gated_group_norm", 0, ly_gated_group_norm_kernel, dim3(Ti, 1), dim3(std::min(1024, std::max(64, (inner + 31) / 32 * 32))), 0,
+               (const float*)y.go.p, (const float*)y.proj.p, lw.n_in, lw.off_g, (const float*)lw.hnorm, eps, inner, 1, 1, y.u.p,
+               lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
     } else if (d.mixer == FL_MIXER_GLA) {
         // decay pre-activation through the rank-r bottleneck: z = W_a2 a (the bias and the sigmoid^(1/tau) are applied by the scan)
         gemm(lc, "gemm_gla_decay", y.proj.p + lw.off_a, lw.n_in, lw.a2, H * D, d.decay_rank, y.la.p, H * D, Ti);
@@ -1091,7 +1177,7 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
     const float* sub_in = canon ? y.hc.p : norm_out;            // what the sublayer's own matrices read
     const size_t hist_stride = y.rows * (size_t)W;
     launch(lc, "embed_norm", 0, ly_embed_norm_kernel, dim3(Ti), dim3(nthr), 0, (const uint16_t*)m.embed, st.tok, W,
-           pre ? (const float*)m.layers[0].norm1 : (const float*)nullptr, eps, plain, (const uint16_t*)m.pos, st.row_pos, y.x.p,
+           pre ? (const float*)m.layers[0].norm1 : (const float*)nullptr, eps, plain, (const uint16_t*)m.pos, st.row_pos, m.cfg.embed_scale, y.x.p,
            depth ? y.xs.p : (float*)nullptr, y.h.p, hhi, hlo);
     // in front of a sublayer: the gate's pre-activation from the normed input, then the input convolution (and its carried inputs)
     auto sublayer_front = [&](const LayeredLayerW& lw, int sub) {
@@ -1114,6 +1200,26 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
             if (taps > 1) launch(lc, "conv_state", 0, ly_conv_state_kernel, dim3(n, (W + 127) / 128), dim3(128), 0, ca);
         }
     };
+    // stacks with a token shift: the mixer reads hc = x + (x_prev - x) * shift (x_prev from the row before, or the slot's carried
+    // row); the slot then keeps this step's last row of x.  The shift kernel rewrites the hi | lo halves with those of hc.
+    const bool shifted = m.cfg.token_shift != 0, sum_norm = m.cfg.post_sum_norm != 0;
+    auto shift_front = [&](const LayeredLayerW& lw, int li) {
+        ConvArgs ca{y.x.p, W, 0, nullptr, nullptr, y.shift_state[li].p, st.row_seq, st.row_pos, st.seq_row0, st.seq_slot, st.seq_pos0, W, 2, nullptr};
+        if (W % 4 == 0)
+            launch(lc, "token_shift", 0, ly_token_shift_kernel<4>, dim3(Ti, (W / 4 + 127) / 128), dim3(128), 0, ca, (const float*)lw.shift, y.hc.p, hhi, hlo);
+        else
+            launch(lc, "token_shift", 0, ly_token_shift_kernel<1>, dim3(Ti, (W + 127) / 128), dim3(128), 0, ca, (const float*)lw.shift, y.hc.p, hhi, hlo);
+        launch(lc, "conv_state", 0, ly_conv_state_kernel, dim3(n, (W + 127) / 128), dim3(128), 0, ca);
+    };
+    // the norm of the sum: x <- norm(alpha x + sa y (+ sb y2)); split: whether another sublayer reads the new x through the tensor cores
+    auto sum_norm_join = [&](const float* yb, const float* y2, float sa, float sb, const float* w, int split) {
+        if (W % 4 == 0)
+            launch(lc, "sum_norm", 0, ly_sum_norm_kernel<4>, dim3(Ti), dim3(std::min(256, std::max(32, (W / 4 + 31) / 32 * 32))), (size_t)W * 4, y.x.p,
+                   (const float*)y.y.p, yb, y2, m.cfg.residual_alpha, sa, sb, w, eps, W, plain, split, hhi, hlo);
+        else
+            launch(lc, "sum_norm", 0, ly_sum_norm_kernel<1>, dim3(Ti), dim3(nthr), (size_t)W * 4, y.x.p, (const float*)y.y.p, yb, y2, m.cfg.residual_alpha, sa, sb,
+                   w, eps, W, plain, split, hhi, hlo);
+    };
     // a sublayer's result (y.y, and y2 beside it) joins the stream; four channels per thread when the rows are 16-byte multiples
     auto join = [&](const float* y2, const float* wa, const float* wb, const float* gate_bias, int hist_slot, const float* dw, const float* wnext) {
         const float* gz = gated ? (const float*)y.gz.p : (const float*)nullptr;
@@ -1129,7 +1235,8 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
         const fl_layer_desc& d = lw.d;
         const int H = d.heads, Dv = d.vdim;
         sublayer_front(lw, 0);
-        gemm_tc_or_exact(c, lc, "gemm_mix_in", sub_in, hhi, hlo, lw.w_in, lw.tm_in, lw.tc_in, lw.n_in, W, y.proj.p, Ti);
+        if (shifted) shift_front(lw, li);
+        gemm_tc_or_exact(c, lc, "gemm_mix_in", shifted ? (const float*)y.hc.p : sub_in, hhi, hlo, lw.w_in, lw.tm_in, lw.tc_in, lw.n_in, W, y.proj.p, Ti);
         run_mixer(c, lc, st, lw, slots, counts, n, h_row0, h_pos0);
         gemm_tc_or_exact(c, lc, "gemm_mix_out", y.u.p, uhi, ulo, lw.w_o, lw.tm_o, lw.tc_o, W, H * Dv, y.y.p, Ti);
         if (lw.side) {
@@ -1140,7 +1247,10 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
         const float* next1 = (pre && li + 1 < m.L) ? m.layers[li + 1].norm1 : nullptr;
         const int more = li + 1 < m.L ? split_x : 0;       // whether another sublayer reads x after this layer
         const bool has_ff = d.ffn != FL_FFN_NONE;
-        if (post)
+        if (sum_norm)
+            sum_norm_join(nullptr, lw.side ? (const float*)y.y2.p : (const float*)nullptr, lw.side ? d.out_scale : 1.f, lw.side ? lw.side->d.out_scale : 0.f,
+                          lw.norm1b, (has_ff || !shifted) ? (has_ff ? split_x : more) : 0);
+        else if (post)
             launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)nullptr, (const float*)lw.norm1b,
                    has_ff ? (const float*)lw.norm2 : next1, eps, W, plain, has_ff ? split_x : more, y.h.p, hhi, hlo);
         else
@@ -1160,8 +1270,9 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
                 launch(lc, "moe_router", 0, ly_router_sigmoid_kernel, dim3(Ti), dim3(256), ((size_t)2 * E + d.route_groups) * 4, sub_in, W, (const float*)lw.router,
                        E, top, (const float*)lw.route_corr, d.route_groups, d.route_keep, y.route_sel.p, y.route_w.p);
             else
-                launch(lc, "moe_router", 0, ly_router_kernel, dim3(Ti), dim3(256), (size_t)E * 4, sub_in, W, (const float*)lw.router, E, top,
+                launch(lc, "moe_router", 0, ly_router_kernel, dim3(Ti), dim3(256), (size_t)E * 4, sub_in, W, (const float*)lw.router, (const float*)lw.router_b, E, top,
                        (const float*)lw.shared_gate, y.route_sel.p, y.route_w.p, y.sgate.p);
+            const float* sg = lw.shared_gate ? (const float*)y.sgate.p : (const float*)nullptr;    // nullptr: the shared expert counts fully
             const float* sh = nullptr;
             if (d.shared_ff > 0) {          // the always-on expert first: its split-K scratch is free again before the routed experts run
                 const int Fs = d.shared_ff;
@@ -1184,7 +1295,7 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
                 }
                 if (sh != nullptr)
                     launch(lc, "moe_accum", 0, ly_moe_accum_kernel, gw, dim3(256), 0, sh, (const int*)nullptr, (const float*)nullptr, 0, -1,
-                           (const float*)y.sgate.p, 0, W, y.y.p);
+                           sg, 0, W, y.y.p);
             } else {
                 launch(lc, "moe_lists", 0, ly_moe_lists_kernel, dim3(E), dim3(32), 0, (const int*)y.route_sel.p, Ti, top, E, y.grp_off.p, y.pair_row.p,
                        y.pair_of.p);
@@ -1201,7 +1312,7 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
                     FL_CHECK((size_t)ks * E * cap * W <= y.gemm_out.n, FL_ERR_STATE, "internal: grouped GEMM scratch too small");
                     launch(lc, "moe_combine", 0, ly_moe_combine_grouped_kernel, gw, dim3(256), 0, (const float*)y.gemm_out.p, ks, (size_t)E * cap * W,
                            (const int*)y.route_sel.p, (const int*)y.pair_of.p, (const int*)y.grp_off.p, cap, (const float*)y.route_w.p, top, sh,
-                           (const float*)y.sgate.p, W, y.y.p);
+                           sg, W, y.y.p);
                 } else {
                     LyGemm g1{sub_in, 0, W, y.pair_row.p, lw.w_gu, (long long)GF * W, GF, W, y.gu.p, 0, GF, y.grp_off.p, P};
                     gemm_groups(lc, "gemm_moe_in", g1, E, P);
@@ -1210,11 +1321,13 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
                     LyGemm g2{y.act.p, 0, F, nullptr, lw.w_down, (long long)W * F, W, F, y.eo.p, 0, W, y.grp_off.p, P};
                     gemm_groups(lc, "gemm_moe_out", g2, E, P);
                     launch(lc, "moe_combine", 0, ly_moe_combine_kernel, gw, dim3(256), 0, (const float*)y.eo.p, (const int*)y.pair_of.p,
-                           (const float*)y.route_w.p, top, sh, (const float*)y.sgate.p, W, y.y.p);
+                           (const float*)y.route_w.p, top, sh, sg, W, y.y.p);
                 }
             }
         }
-        if (post)
+        if (sum_norm)
+            sum_norm_join(lw.b_down, nullptr, 1.f, 0.f, lw.norm2b, shifted ? 0 : more);
+        else if (post)
             launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.b_down, (const float*)lw.norm2b,
                    next1, eps, W, plain, more, y.h.p, hhi, hlo);
         else
@@ -1224,6 +1337,11 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
         launch(lc, "final_norm", 0, ly_final_norm_kernel, dim3(n_want), dim3(nthr), 0, (const float*)y.x.p, st.want, (const float*)m.final_norm, eps, W, plain, y.hf.p,
                m.tc_head ? y.hf_hi.p : (uint16_t*)nullptr, y.hf_lo.p);
         gemm_tc_or_exact(c, lc, "gemm_head", y.hf.p, m.tc_head ? y.hf_hi.p : nullptr, y.hf_lo.p, m.head, m.tm_head, m.tc_head, m.V, W, y.logits.p, n_want);
+        if (m.cfg.logit_softcap > 0.f) {
+            const size_t nl = (size_t)n_want * m.V;
+            launch(lc, "logit_cap", 0, ly_softcap_kernel, dim3((unsigned)std::min<size_t>(4 * kNumSMs, (nl + 255) / 256)), dim3(256), 0, y.logits.p, nl,
+                   m.cfg.logit_softcap);
+        }
     }
 }
 

@@ -1,8 +1,9 @@
-// Layered decoders (FL_ARCH_NIFUNEX, FL_ARCH_ROFETAR, FL_ARCH_TOZARAX): model / cache objects shared by fl_layered.cu and fl_lib.cu.
-// A layer = one mixer (gated linear attention | latent attention | grouped-query attention | Mamba-2 | gated delta rule), or two
-// of them side by side, + an optional feed-forward (dense | MoE), each wrapped by a norm before and after, after only
-// (fl_stack_config.no_pre_norm) or before only (no_post_norm); optionally a learned position table, an input convolution in front of
-// every sublayer, a gate on every sublayer's contribution and an average over all earlier layers' outputs.  Sizes and constants
+// Layered decoders (FL_ARCH_NIFUNEX, FL_ARCH_ROFETAR, FL_ARCH_TOZARAX, FL_ARCH_MEDULORN): model / cache objects shared by fl_layered.cu and
+// fl_lib.cu.  A layer = one mixer (gated linear attention | latent attention | grouped-query attention | Mamba-2 | gated delta rule |
+// lightning attention), or two of them side by side, + an optional feed-forward (dense | MoE), each wrapped by a norm before and
+// after, after only (fl_stack_config.no_pre_norm), before only (no_post_norm), or a norm of the sum of stream and sublayer result
+// (post_sum_norm); optionally a learned position table, an input convolution in front of every sublayer, a token shift in front of
+// every mixer, a gate on every sublayer's contribution and an average over all earlier layers' outputs.  Sizes and constants
 // come from fl_layer_desc / fl_stack_config; nothing is fixed per model.
 #pragma once
 #include <cuda.h>
@@ -33,7 +34,12 @@ struct LayeredLayerW {
     int conv_off = 0, conv_ch = 0;      // recurrent mixers with a short convolution: the convolved columns of w_in's output
     float *conv_w = nullptr, *conv_b = nullptr;                                         // [conv_ch, taps], [conv_ch] (zeros when the design has none)
     float *a_log = nullptr, *dt_bias = nullptr, *dskip = nullptr;                       // [heads]
-    float *qnorm = nullptr, *knorm = nullptr;                                           // attention: [dim]
+    float *qnorm = nullptr, *knorm = nullptr;                                           // attention: [dim] ([heads * dim], [kv_heads * dim] with qk_norm_whole)
+    float *bq = nullptr, *bk = nullptr, *bv = nullptr;                                  // attention with qkv_bias: [heads * dim], [kv_heads * dim], [kv_heads * vdim]
+    float* sinkv = nullptr;                                                             // attention with a learned sink: [heads]
+    float* decay = nullptr;                                                             // lightning attention: [heads], f32 as given
+    float* shift = nullptr;                                                             // token shift: [W]
+    float* router_b = nullptr;                                                          // biased router: [experts]
     float *b_gu = nullptr, *b_down = nullptr;                                           // biased dense feed-forward: [2 ff], [W]
     uint16_t* w_o = nullptr;            // [W, heads * vdim]
     // GLA
@@ -75,9 +81,10 @@ struct RopeSpec {                       // one distinct rotary configuration (ta
     int dims = 0;
     double base = 0;
     float yarn_factor = 0, yarn_original = 0, yarn_fast = 0, yarn_slow = 0;
+    int scaling = 0;                    // fl_rot_scaling
     bool operator==(const RopeSpec& o) const {
         return dims == o.dims && base == o.base && yarn_factor == o.yarn_factor && yarn_original == o.yarn_original &&
-               yarn_fast == o.yarn_fast && yarn_slow == o.yarn_slow;
+               yarn_fast == o.yarn_fast && yarn_slow == o.yarn_slow && scaling == o.scaling;
     }
 };
 
@@ -112,6 +119,7 @@ struct LayeredCache {
     std::vector<DevBuf<float>> gla_state;          // per recurrent layer: [slots][heads][dim | state][vdim]
     std::vector<DevBuf<float>> conv_state;         // per recurrent layer: [slots][taps - 1][conv_ch] (empty without a convolution)
     std::vector<DevBuf<float>> canon_state;        // input convolutions: per layer [2 sublayers][slots][taps - 1][W]
+    std::vector<DevBuf<float>> shift_state;        // token shift: per layer [slots][W], the mixer input of the slot's last position
     std::vector<DevBuf<float>> rope_cos, rope_sin; // per RopeSpec: [max_seq][dims/2]
     DevBuf<int> page_table;             // [slots][pages_per_slot]
     DevBuf<int> step_tab;               // per-step integer tables (see StepTab in fl_layered.cu)

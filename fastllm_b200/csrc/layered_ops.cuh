@@ -108,13 +108,13 @@ static __global__ void ly_sum_slices_kernel(const float* __restrict__ y, int nsl
 // A norm weight w scales by (1 + w), or by w itself when `plain`.
 __device__ __forceinline__ float norm_scale(const float* __restrict__ w, int c, int plain) { return plain ? w[c] : 1.f + w[c]; }
 
-// x[row] = embed[tok[row]] (+ pos_tab[row_pos[row]], a learned position vector);  h[row] = x / sqrt(mean x^2 + eps) * scale(w).
+// x[row] = embed[tok[row]] (times escale when that is not 0) (+ pos_tab[row_pos[row]], a learned position vector);  h[row] = x / sqrt(mean x^2 + eps) * scale(w).
 // nw == nullptr (the first sublayer reads the stream itself): h is not written and the hi | lo halves are those of x.
 // x0 (optional): a second copy of x, the first entry of the depth average's history.
 static __global__ void ly_embed_norm_kernel(const uint16_t* __restrict__ embed, const int* __restrict__ tok, int W, const float* __restrict__ nw,
                                             float eps, int plain, const uint16_t* __restrict__ pos_tab, const int* __restrict__ row_pos,
-                                            float* __restrict__ x, float* __restrict__ x0, float* __restrict__ h, uint16_t* __restrict__ hhi,
-                                            uint16_t* __restrict__ hlo) {
+                                            float escale, float* __restrict__ x, float* __restrict__ x0, float* __restrict__ h,
+                                            uint16_t* __restrict__ hhi, uint16_t* __restrict__ hlo) {
     __shared__ float red[33];
     const int row = blockIdx.x;
     const uint16_t* e = embed + (size_t)tok[row] * W;
@@ -123,6 +123,7 @@ static __global__ void ly_embed_norm_kernel(const uint16_t* __restrict__ embed, 
     float ss = 0.f;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float v = __uint_as_float((uint32_t)e[c] << 16);
+        if (escale != 0.f) v *= escale;
         if (pe) v += __uint_as_float((uint32_t)pe[c] << 16);
         xr[c] = v;
         if (x0) x0[(size_t)row * W + c] = v;
@@ -249,6 +250,57 @@ static __global__ void ly_join_kernel(float* __restrict__ x, const float* __rest
         st_vec<V>(h + rb + c, t);
         split_store_vec<V>(hhi, hlo, rb + c, t);
     }
+}
+
+// The norm follows the sum:  x[row] <- unit(alpha x[row] + sa (y[row] + yb) + sb y2[row]) * w,  unit(v) = v / sqrt(mean v^2 + eps); y2 and
+// yb are optional.  split_x: also the hi | lo halves of the new x (the next sublayer reads the stream itself).  One block per row, V
+// consecutive channels per thread (V = 4: 16-byte accesses, W a multiple of 4); the summed row waits in shared memory ([W] floats)
+// between the two passes.
+template <int V>
+static __global__ void ly_sum_norm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ yb, const float* __restrict__ y2,
+                                          float alpha, float sa, float sb, const float* __restrict__ w, float eps, int W, int plain, int split_x,
+                                          uint16_t* __restrict__ hhi, uint16_t* __restrict__ hlo) {
+    extern __shared__ __align__(16) float srow[];
+    __shared__ float red[33];
+    const size_t rb = (size_t)blockIdx.x * W;
+    const int step = blockDim.x * V;
+    float ss = 0.f;
+    for (int c = threadIdx.x * V; c < W; c += step) {
+        float t[V], p[V];
+        ld_vec<V>(x + rb + c, t); ld_vec<V>(y + rb + c, p);
+        if (yb != nullptr) {
+            float b[V];
+            ld_vec<V>(yb + c, b);
+#pragma unroll
+            for (int i = 0; i < V; ++i) p[i] += b[i];
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) t[i] = fmaf(alpha, t[i], sa * p[i]);
+        if (y2 != nullptr) {
+            float q[V];
+            ld_vec<V>(y2 + rb + c, q);
+#pragma unroll
+            for (int i = 0; i < V; ++i) t[i] = fmaf(sb, q[i], t[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) ss += t[i] * t[i];
+        st_vec<V>(srow + c, t);
+    }
+    const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
+    for (int c = threadIdx.x * V; c < W; c += step) {
+        float t[V], wn[V];
+        ld_vec<V>(srow + c, t); ld_vec<V>(w + c, wn);
+#pragma unroll
+        for (int i = 0; i < V; ++i) t[i] = t[i] * r * (plain ? wn[i] : 1.f + wn[i]);
+        st_vec<V>(x + rb + c, t);
+        if (split_x) split_store_vec<V>(hhi, hlo, rb + c, t);
+    }
+}
+
+// logits <- cap tanh(logits / cap)
+static __global__ void ly_softcap_kernel(float* __restrict__ z, size_t n, float cap) {
+    const float inv = 1.f / cap;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) z[i] = cap * tanhf(z[i] * inv);
 }
 
 // hf[i] = norm(x[want[i]]; w): the rows that go on to the vocabulary projection
@@ -650,26 +702,49 @@ static __global__ void ly_attn_build_q_kernel(const float* __restrict__ qa, cons
         split_store(qhi, qlo, base + c, v);
     }
 }
-// P[r, col] = softmax over the keys the row's position admits (0 <= pos - j < window, j = k_lo + col), zero elsewhere; row r belongs
-// to token r / H of the block.  softcap > 0: scores pass softcap * tanh(s / softcap) first; sink: the denominator gets exp(0) more.
-// The (capped) scores of the row are kept in shared memory after the first pass when `keep` floats of it were given to the launch
-// and the row fits (a thread meets the same columns in every pass, so it reads back what it wrote itself).
-static __global__ void ly_attn_softmax_kernel(const float* __restrict__ S, const int* __restrict__ row_pos, int row0, int H, int k_lo, int nk, int nkp,
-                                              int window, float softcap, int sink, int keep, uint16_t* __restrict__ phi, uint16_t* __restrict__ plo) {
+// Which keys position `pos` reads: with lo_c the start of its chunk (0 without chunks) and lo_w the start of its window (0 without one),
+// the contiguous range [j0, pos], j0 = max(lo_w, lo_c), and before it the kept first keys [s_lo, s_hi) = [lo_c, min(keep_first, j0))
+// (empty unless a window is set and s_lo < s_hi).
+struct KeySpan { int j0, s_lo, s_hi; };
+__device__ __forceinline__ KeySpan key_span(int pos, int window, int keep_first, int chunk) {
+    const int lo_c = chunk > 0 ? pos / chunk * chunk : 0;
+    const int lo_w = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    KeySpan k;
+    k.j0 = max(lo_w, lo_c);
+    k.s_lo = lo_c;
+    k.s_hi = window > 0 ? max(lo_c, min(keep_first, k.j0)) : lo_c;
+    return k;
+}
+
+// P[r, col] = softmax over the keys the row's position admits (key_span), zero elsewhere; row r belongs to token r / H of the block.
+// Columns: the first n_first hold keys 0 .. n_first - 1 (kept first keys that lie before k_lo), column n_first + i holds key k_lo + i,
+// i < nk.  softcap > 0: scores pass softcap * tanh(s / softcap) first; sink: the denominator gets exp(sinkv[r % H]) more (exp(0) when
+// sinkv is nullptr).  The (capped) scores of the row are kept in shared memory after the first pass when `keep` floats of it were
+// given to the launch and the row fits (a thread meets the same columns in every pass, so it reads back what it wrote itself).
+static __global__ void ly_attn_softmax_kernel(const float* __restrict__ S, const int* __restrict__ row_pos, int row0, int H, int k_lo, int n_first, int nk,
+                                              int nkp, int window, int keep_first, int chunk, float softcap, int sink, const float* __restrict__ sinkv,
+                                              int keep, uint16_t* __restrict__ phi, uint16_t* __restrict__ plo) {
     extern __shared__ float srow[];
     __shared__ float red[33];
     const size_t r = blockIdx.x;
     const int pos = row_pos[row0 + (int)(r / H)];
-    const int j_first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int c_lo = j_first > k_lo ? j_first - k_lo : 0, c_hi = min(nk, pos - k_lo + 1);      // visible columns [c_lo, c_hi)
+    const KeySpan ks = key_span(pos, window, keep_first, chunk);
+    // visible columns: [a_lo, a_hi) of the first part; of [b_lo, c_hi) in the main part those whose key passes `vis`
+    const int a_lo = min(ks.s_lo, n_first), a_hi = min(ks.s_hi, n_first), na = a_hi - a_lo;
+    const int first_main = ks.s_hi > max(ks.s_lo, k_lo) ? max(ks.s_lo, k_lo) : ks.j0;
+    const int b_lo = n_first + max(first_main - k_lo, 0), c_hi = n_first + min(nk, pos - k_lo + 1);
+    auto vis = [&](int c) { const int j = k_lo + c - n_first; return j >= ks.j0 || (j >= ks.s_lo && j < ks.s_hi); };
     const float* sr = S + r * nkp;
     const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
-    const bool kept = c_hi - c_lo <= keep;
+    const int nvis = na + max(c_hi - b_lo, 0);
+    const bool kept = nvis <= keep;
+    const float sv = sink ? (sinkv ? sinkv[r % H] : 0.f) : 0.f;
     auto score = [&](int c) { const float v = sr[c]; return softcap > 0.f ? softcap * tanhf(v * inv_cap) : v; };
-    float m = sink ? 0.f : -INFINITY;
-    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) {
-        const float v = score(c);
-        if (kept) srow[c - c_lo] = v;
+    float m = sink ? sv : -INFINITY;
+    for (int i = threadIdx.x; i < nvis; i += blockDim.x) {
+        const int c = i < na ? a_lo + i : b_lo + (i - na);
+        const float v = (i < na || vis(c)) ? score(c) : -INFINITY;
+        if (kept) srow[i] = v;
         m = fmaxf(m, v);
     }
     m = warp_max(m);
@@ -682,15 +757,20 @@ static __global__ void ly_attn_softmax_kernel(const float* __restrict__ S, const
         m = warp_max(t);
     }
     float sum = 0.f;
-    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) {
-        const float e = expf((kept ? srow[c - c_lo] : score(c)) - m);
-        if (kept) srow[c - c_lo] = e;
+    for (int i = threadIdx.x; i < nvis; i += blockDim.x) {
+        const int c = i < na ? a_lo + i : b_lo + (i - na);
+        const float v = kept ? srow[i] : ((i < na || vis(c)) ? score(c) : -INFINITY);
+        const float e = v == -INFINITY ? 0.f : expf(v - m);
+        if (kept) srow[i] = e;
         sum += e;
     }
-    const float inv = 1.f / (block_sum(sum, red) + (sink ? expf(-m) : 0.f));
+    const float inv = 1.f / (block_sum(sum, red) + (sink ? expf(sv - m) : 0.f));
     for (int c = threadIdx.x; c < nkp; c += blockDim.x) {
         float p = 0.f;
-        if (c >= c_lo && c < c_hi) p = (kept ? srow[c - c_lo] : expf(score(c) - m)) * inv;
+        int i = -1;
+        if (c >= a_lo && c < a_hi) i = c - a_lo;
+        else if (c >= b_lo && c < c_hi && c >= n_first && vis(c)) i = na + (c - b_lo);
+        if (i >= 0) p = (kept ? srow[i] : expf(score(c) - m)) * inv;
         split_store(phi, plo, r * nkp + c, p);
     }
 }
@@ -699,20 +779,44 @@ static __global__ void ly_attn_softmax_kernel(const float* __restrict__ S, const
 // Cache row of a token: [kv_heads][dim] keys (normed, rotated) then [kv_heads][vdim] values.
 struct AttnPrepArgs {
     float* proj; int ldp, off_q, off_k, off_v;  // off_k < 0: the layer reads another layer's cache (queries are still prepared)
-    const float *qnorm, *knorm; float eps;       // [dim] each
+    const float *qnorm, *knorm; float eps;       // [dim] each ([H * dim], [G * dim] when `whole`)
     void* pool; const int* page_table; int pps;
     const int *row_seq, *row_pos, *seq_slot;
     const float *cosb, *sinb;                    // [max_seq][rdims / 2], already multiplied by the YaRN magnitude
     int H, G, D, Dv, rdims, halves;
+    const float *bq, *bk, *bv;                   // projection biases [H * dim], [G * dim], [G * vdim] (nullptr: none)
+    int whole;                                   // 1: q (and k) are normed over all heads' channels at once
 };
 // Per row: every query head and (when the layer owns its cache) every key head is RMS-normed over dim with a weight shared by the
 // heads (qnorm == nullptr: they are used as projected), then its first rdims channels are turned by the row's position: pairs (i, i + rdims/2) when `halves`, else (2i, 2i+1).
-// Queries are rewritten in place, keys and values go to the row's cache page.  One warp per head in turn.
+// Queries are rewritten in place, keys and values go to the row's cache page.  One warp per head in turn.  Biases, when the
+// projections have them, are added first (in place); with `whole` the mean square is taken over all heads of q (of k) and the weight
+// is indexed by the channel inside the whole projection.
 template <typename CT>
 static __global__ void __launch_bounds__(128) ly_attn_prep_kernel(AttnPrepArgs a) {
     extern __shared__ float sm[];               // [4 warps][D]
+    __shared__ float red[33];
     const int row = blockIdx.x, pos = a.row_pos[row], lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     float* pr = a.proj + (size_t)row * a.ldp;
+    if (a.bq != nullptr) {
+        for (int c = threadIdx.x; c < a.H * a.D; c += blockDim.x) pr[a.off_q + c] += a.bq[c];
+        if (a.off_k >= 0) {
+            for (int c = threadIdx.x; c < a.G * a.D; c += blockDim.x) pr[a.off_k + c] += a.bk[c];
+            for (int c = threadIdx.x; c < a.G * a.Dv; c += blockDim.x) pr[a.off_v + c] += a.bv[c];
+        }
+        __syncthreads();
+    }
+    float rq = 0.f, rk = 0.f;
+    if (a.whole && a.qnorm != nullptr) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < a.H * a.D; c += blockDim.x) ss += pr[a.off_q + c] * pr[a.off_q + c];
+        rq = 1.f / sqrtf(block_sum(ss, red) / (float)(a.H * a.D) + a.eps);
+        if (a.off_k >= 0) {
+            ss = 0.f;
+            for (int c = threadIdx.x; c < a.G * a.D; c += blockDim.x) ss += pr[a.off_k + c] * pr[a.off_k + c];
+            rk = 1.f / sqrtf(block_sum(ss, red) / (float)(a.G * a.D) + a.eps);
+        }
+    }
     const int half = a.rdims / 2;
     const float* cs = a.cosb + (size_t)pos * half;
     const float* sn = a.sinb + (size_t)pos * half;
@@ -729,7 +833,11 @@ static __global__ void __launch_bounds__(128) ly_attn_prep_kernel(AttnPrepArgs a
         const bool isq = it < a.H;
         float* src = isq ? pr + a.off_q + it * a.D : pr + a.off_k + (it - a.H) * a.D;
         const float* w = isq ? a.qnorm : a.knorm;
-        if (w != nullptr) {
+        if (w != nullptr && a.whole) {
+            const float r = isq ? rq : rk;
+            w += (size_t)(isq ? it : it - a.H) * a.D;
+            for (int c = lane; c < a.D; c += 32) buf[c] = src[c] * r * w[c];
+        } else if (w != nullptr) {
             float ss = 0.f;
             for (int c = lane; c < a.D; c += 32) ss += src[c] * src[c];
             const float r = 1.f / sqrtf(warp_sum(ss) / (float)a.D + a.eps);
@@ -767,14 +875,17 @@ struct GqaAttnArgs {
     uint16_t *ohi, *olo;        // its hi | lo halves (nullptr: not wanted)
     int H, G, D, Dv, window;
     float scale, softcap;       // softcap 0 = scores are used as they are
-    int sink;                   // 1: the denominator gets exp(0) more
+    int sink;                   // != 0: the denominator gets exp(sinkv[head]) more (exp(0) when sinkv is nullptr)
     int row_base;
     float* part;                // key splits (gridDim.z > 1): [T][H][splits][2 + Dv] partial (max, sum, weighted values)
+    int keep_first, chunk;      // masks beside the window (see key_span)
+    const float* sinkv;         // [H] or nullptr
 };
 constexpr int kGqaWarps = 8;
-// One block per (row, RB query heads of one key/value head, key split).  score_j = cap(q . k_j * scale) over the keys j <= pos (and
-// inside the window, if any), softmax in f32 with the optional sink, out = sum_j p_j v_j.  The 8 x splits warps of a (row, head
-// group) take the keys round-robin: warp v folds keys j0 + v, j0 + v + 8 splits, ... into an online softmax per head (lanes own
+// One block per (row, RB query heads of one key/value head, key split).  score_j = cap(q . k_j * scale) over the keys the position
+// admits (key_span: causal, window with kept first keys, chunk), softmax in f32 with the optional sink, out = sum_j p_j v_j.  The
+// 8 x splits warps of a (row, head group) take the visible keys round-robin in ascending order: warp v folds the v-th, (v + 8 splits)-th,
+// ... visible key into an online softmax per head (lanes own
 // CPL consecutive channels of the key and of the value; a key and its value are loaded once for the RB heads).  Partial results
 // are merged in warp order; with one split the block writes the output itself (which warp takes which key then depends on the
 // position alone), otherwise ly_gqa_merge_kernel folds the splits in order.
@@ -786,7 +897,8 @@ static __global__ void __launch_bounds__(kGqaWarps * 32) ly_gqa_attn_kernel(GqaA
     const int D = a.D, Dv = a.Dv, g = hd0 / (a.H / a.G);
     const size_t E = (size_t)a.G * (D + Dv);
     const int pos = a.row_pos[row], slot = a.seq_slot[a.row_seq[row]];
-    const int j0 = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    const KeySpan ks = key_span(pos, a.window, a.keep_first, a.chunk);
+    const int n_st = ks.s_hi - ks.s_lo, n_vis = n_st + pos - ks.j0 + 1;        // kept first keys, then the contiguous range
     float q[RB][CPL], acc[RB][CPL], m[RB], l[RB];
 #pragma unroll
     for (int r = 0; r < RB; ++r) {
@@ -799,14 +911,14 @@ static __global__ void __launch_bounds__(kGqaWarps * 32) ly_gqa_attn_kernel(GqaA
     const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
     constexpr int KU = 2;
     const int stride = kGqaWarps * S;
-    for (int j = j0 + split * kGqaWarps + wid; j <= pos; j += stride * KU) {
+    for (int j = split * kGqaWarps + wid; j < n_vis; j += stride * KU) {
         float val[KU][CPL], dot[KU][RB];
 #pragma unroll
         for (int u = 0; u < KU; ++u) {
-            const int jj = j + u * stride;
+            const int ji = j + u * stride, jj = ji < n_st ? ks.s_lo + ji : ks.j0 + (ji - n_st);
 #pragma unroll
             for (int r = 0; r < RB; ++r) dot[u][r] = 0.f;
-            if (jj <= pos) {
+            if (ji < n_vis) {
                 const CT* kp = (const CT*)a.pool + ((size_t)pt[jj / kKvPage] * kKvPage + jj % kKvPage) * E;
                 float kk[CPL];
                 load_chunk<CPL>(kp + (size_t)g * D, lane * CPL, D, kk);
@@ -826,7 +938,7 @@ static __global__ void __launch_bounds__(kGqaWarps * 32) ly_gqa_attn_kernel(GqaA
             for (int r = 0; r < RB; ++r) dot[u][r] = warp_sum(dot[u][r]);
 #pragma unroll
         for (int u = 0; u < KU; ++u) {
-            if (j + u * stride > pos) break;
+            if (j + u * stride >= n_vis) break;
 #pragma unroll
             for (int r = 0; r < RB; ++r) {
                 float sc = dot[u][r];
@@ -849,10 +961,11 @@ static __global__ void __launch_bounds__(kGqaWarps * 32) ly_gqa_attn_kernel(GqaA
     }
     __syncthreads();
     for (int r = 0; r < RB; ++r) {
-        float M = (S == 1 && a.sink) ? 0.f : -INFINITY;
+        const float sv = a.sinkv ? a.sinkv[hd0 + r] : 0.f;
+        float M = (S == 1 && a.sink) ? sv : -INFINITY;
 #pragma unroll
         for (int w = 0; w < kGqaWarps; ++w) M = fmaxf(M, sml[(w * RB + r) * 2]);
-        float f[kGqaWarps], Lsum = (S == 1 && a.sink) ? expf(-M) : 0.f;
+        float f[kGqaWarps], Lsum = (S == 1 && a.sink) ? expf(sv - M) : 0.f;
 #pragma unroll
         for (int w = 0; w < kGqaWarps; ++w) {
             const float mw = sml[(w * RB + r) * 2];
@@ -883,13 +996,14 @@ static __global__ void __launch_bounds__(kGqaWarps * 32) ly_gqa_attn_kernel(GqaA
     }
 }
 // Folds the key splits of ly_gqa_attn_kernel in split order (and the sink): one block per (row, head).
-static __global__ void ly_gqa_merge_kernel(const float* __restrict__ part, int S, int H, int Dv, int sink, int row_base, float* __restrict__ out,
-                                           uint16_t* __restrict__ ohi, uint16_t* __restrict__ olo) {
+static __global__ void ly_gqa_merge_kernel(const float* __restrict__ part, int S, int H, int Dv, int sink, const float* __restrict__ sinkv, int row_base,
+                                           float* __restrict__ out, uint16_t* __restrict__ ohi, uint16_t* __restrict__ olo) {
     const int row = row_base + blockIdx.x, hd = blockIdx.y;
     const float* pp = part + ((size_t)blockIdx.x * H + hd) * S * (Dv + 2);
-    float M = sink ? 0.f : -INFINITY;
+    const float sv = sinkv ? sinkv[hd] : 0.f;
+    float M = sink ? sv : -INFINITY;
     for (int s = 0; s < S; ++s) M = fmaxf(M, pp[(size_t)s * (Dv + 2)]);
-    float L = sink ? expf(-M) : 0.f;
+    float L = sink ? expf(sv - M) : 0.f;
     for (int s = 0; s < S; ++s) {
         const float ms = pp[(size_t)s * (Dv + 2)];
         L += ms == -INFINITY ? 0.f : pp[(size_t)s * (Dv + 2) + 1] * expf(ms - M);
@@ -912,12 +1026,13 @@ static __global__ void ly_gqa_merge_kernel(const float* __restrict__ part, int S
 // Per block of consecutive query rows of ONE sequence and per key/value head g: the keys the block can reach are gathered once
 // (Kc [nkp, Dp], zero padded) with the values transposed (Vt [Dv, nkp]); the rows of the score GEMM are (token, query head of
 // the group) pairs -- all of them meet the same keys --, S = Q . Kc^T, P = masked softmax(S) (cap, sink), O = P . V.
-static __global__ void ly_gqa_gather_kv_kernel(const uint16_t* __restrict__ pool, const int* __restrict__ page_row, int k_lo, int nk, int nkp, int E,
-                                               int koff, int D, int Dp, int voff, int Dv, uint16_t* __restrict__ kc, uint16_t* __restrict__ vt) {
+// Rows r < n_first hold keys 0 .. n_first - 1 (kept first keys before k_lo), rows n_first + i key k_lo + i, i < nk.
+static __global__ void ly_gqa_gather_kv_kernel(const uint16_t* __restrict__ pool, const int* __restrict__ page_row, int k_lo, int n_first, int nk, int nkp,
+                                               int E, int koff, int D, int Dp, int voff, int Dv, uint16_t* __restrict__ kc, uint16_t* __restrict__ vt) {
     const int r = blockIdx.x;
     const uint16_t* src = nullptr;
-    if (r < nk) {
-        const int j = k_lo + r;
+    if (r < n_first + nk) {
+        const int j = r < n_first ? r : k_lo + (r - n_first);
         src = pool + ((size_t)page_row[j / kKvPage] * kKvPage + j % kKvPage) * E;
     }
     for (int c = threadIdx.x; c < Dp; c += blockDim.x) kc[(size_t)r * Dp + c] = (src != nullptr && c < D) ? src[koff + c] : (uint16_t)0;
@@ -981,6 +1096,44 @@ static __global__ void ly_conv_state_kernel(ConvArgs a) {
     const int last_row = r0 + n - 1, last_pos = pos0 + n - 1;
     for (int i = 0; i < a.taps - 1; ++i) keep[i] = conv_input(a, last_row, r0, last_pos, pos0, slot, a.taps - 2 - i, c);
     for (int i = 0; i < a.taps - 1; ++i) a.state[((size_t)slot * (a.taps - 1) + i) * a.ch + c] = keep[i];
+}
+
+// Token shift in front of a mixer: out[row, c] = in[row, c] + (prev - in[row, c]) * mu[c], prev = the same channel of the sequence's
+// previous position (a row of this step, the slot's carried row -- ConvArgs with taps = 2 --, or zero at position 0), with the hi | lo
+// halves.  grid (rows, channel blocks of 128 x V); V = 4: 16-byte accesses (ch, ldp, off multiples of 4).
+template <int V>
+static __global__ void __launch_bounds__(128) ly_token_shift_kernel(ConvArgs a, const float* __restrict__ mu, float* __restrict__ out,
+                                                                      uint16_t* __restrict__ ohi, uint16_t* __restrict__ olo) {
+    const int row = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    if (c >= a.ch) return;
+    const int seq = a.row_seq[row], pos = a.row_pos[row];
+    float cur[V], prev[V], m[V];
+    ld_vec<V>(a.proj + (size_t)row * a.ldp + a.off + c, cur);
+    ld_vec<V>(mu + c, m);
+    if (row - 1 >= a.seq_row0[seq]) ld_vec<V>(a.proj + (size_t)(row - 1) * a.ldp + a.off + c, prev);
+    else if (pos > 0) ld_vec<V>(a.state + (size_t)a.seq_slot[seq] * a.ch + c, prev);
+    else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) prev[i] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) cur[i] = cur[i] + (prev[i] - cur[i]) * m[i];
+    st_vec<V>(out + (size_t)row * a.ch + c, cur);
+    split_store_vec<V>(ohi, olo, (size_t)row * a.ch + c, cur);
+}
+
+// Lightning attention, per row: q | k | v <- silu(projection) (the columns proj[row, off .. off + ch) -> cv[row, :]); per head
+// ab[row, h] = (decay[h], 1): the scan's fixed fade and a write strength of one.  grid (rows, channel chunks of `chunk`).
+static __global__ void ly_lightning_prep_kernel(const float* __restrict__ proj, int ldp, int off, int ch, int chunk, const float* __restrict__ decay, int H,
+                                                float* __restrict__ cv, float* __restrict__ ab) {
+    const int row = blockIdx.x, c0 = blockIdx.y * chunk, c1 = min(ch, c0 + chunk);
+    const float* pr = proj + (size_t)row * ldp + off;
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) cv[(size_t)row * ch + c] = siluf_(pr[c]);
+    if (blockIdx.y != 0) return;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        ab[((size_t)row * H + h) * 2] = decay[h];
+        ab[((size_t)row * H + h) * 2 + 1] = 1.f;
+    }
 }
 
 // The input convolution in front of a sublayer: out[row, c] = in[row, c] + sum_k w[c, k] * in[position - (taps - 1 - k), c] (no bias,
@@ -1191,18 +1344,20 @@ static __global__ void __launch_bounds__(128) ly_rec_scan_kernel(RecArgs a) {
 
 // u[row, part] = v / sqrt(mean_part v^2 + eps) * w,  v = y * silu(z): the gated output of Mamba-2, normed in `parts` equal pieces of
 // the inner width.  z = proj[row, off_z ...].  One block per (row, part).
+// sig_after: u[row, part] = y / sqrt(mean_part y^2 + eps) * w * sigmoid(z) instead -- the norm sees the scan's output itself and the
+// gate follows it (lightning attention, parts = 1).
 static __global__ void ly_gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ proj, int ldp, int off_z,
-                                                  const float* __restrict__ w, float eps, int inner, int parts, float* __restrict__ u,
+                                                  const float* __restrict__ w, float eps, int inner, int parts, int sig_after, float* __restrict__ u,
                                                   uint16_t* __restrict__ uhi, uint16_t* __restrict__ ulo) {
     __shared__ float red[33];
     const int row = blockIdx.x, n = inner / parts, c0 = blockIdx.y * n;
     const float* yr = y + (size_t)row * inner + c0;
     const float* zr = proj + (size_t)row * ldp + off_z + c0;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < n; c += blockDim.x) { const float v = yr[c] * siluf_(zr[c]); ss += v * v; }
+    for (int c = threadIdx.x; c < n; c += blockDim.x) { const float v = sig_after ? yr[c] : yr[c] * siluf_(zr[c]); ss += v * v; }
     const float r = 1.f / sqrtf(block_sum(ss, red) / (float)n + eps);
     for (int c = threadIdx.x; c < n; c += blockDim.x) {
-        const float v = yr[c] * siluf_(zr[c]) * r * w[c0 + c];
+        const float v = sig_after ? yr[c] * r * w[c0 + c] * sigmoidf_(zr[c]) : yr[c] * siluf_(zr[c]) * r * w[c0 + c];
         u[(size_t)row * inner + c0 + c] = v;
         split_store(uhi, ulo, (size_t)row * inner + c0 + c, v);
     }
@@ -1211,9 +1366,10 @@ static __global__ void ly_gated_group_norm_kernel(const float* __restrict__ y, c
 // ---- feed-forward ----------------------------------------------------------------------------------------------------------
 // act 0: act[p, f] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[p, f], limit),  u = clamp(gu[p, F + f], -limit, limit);
 // act 1: act[p, f] = gelu_tanh(g) * u,  gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  bias [2F] (optional) is added
-// to gate | up first.  act 2: act[p, f] = relu(gu[p, f])^2 -- no gate matrix, gu has F columns.  p < *count
+// to gate | up first.  act 2: act[p, f] = relu(gu[p, f])^2 -- no gate matrix, gu has F columns.  act 3: act[p, f] = relu(g) * u.  p < *count
 __device__ __forceinline__ float glu_value(float g, float u, int act, float limit) {
     if (act == 2) { g = fmaxf(g, 0.f); return g * g; }
+    if (act == 3) return fmaxf(g, 0.f) * u;
     if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
@@ -1237,8 +1393,9 @@ static __global__ void ly_glu_kernel(const float* __restrict__ gu, int F, float 
 
 // Router: z = Wr h (f32), s = softmax(z) over all experts, the `top` largest (lower index first among equals), weights s / (sum + 1e-20).
 // Also the shared expert's gate sigmoid(w_sg . h).  One block per row, one warp per expert in turn.
-static __global__ void ly_router_kernel(const float* __restrict__ h, int W, const float* __restrict__ wr, int E, int top, const float* __restrict__ wsg,
-                                        int* __restrict__ sel, float* __restrict__ wt, float* __restrict__ sgate) {
+// rb (optional): a bias [E] added to the logits.  (Softmax over all, then renormalised over the chosen = softmax over the chosen alone.)
+static __global__ void ly_router_kernel(const float* __restrict__ h, int W, const float* __restrict__ wr, const float* __restrict__ rb, int E, int top,
+                                        const float* __restrict__ wsg, int* __restrict__ sel, float* __restrict__ wt, float* __restrict__ sgate) {
     extern __shared__ float z[];                 // [E]
     const int row = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const float* hr = h + (size_t)row * W;
@@ -1258,7 +1415,7 @@ static __global__ void ly_router_kernel(const float* __restrict__ h, int W, cons
         }
         d = warp_sum(d);
         if (lane == 0) {
-            if (e < E) z[e] = d; else sgate[row] = sigmoidf_(d);
+            if (e < E) z[e] = d + (rb ? rb[e] : 0.f); else sgate[row] = sigmoidf_(d);
         }
     }
     __syncthreads();
@@ -1421,7 +1578,7 @@ static __global__ void ly_moe_combine_grouped_kernel(const float* __restrict__ e
             for (int sl = 0; sl < nsl; ++sl) v += eo[sl * sl_stride + r * W + c];
             t = fmaf(wt[row * top + k], v, t);
         }
-        if (sh != nullptr) t = fmaf(sgate[row], sh[(size_t)row * W + c], t);
+        if (sh != nullptr) t = fmaf(sgate ? sgate[row] : 1.f, sh[(size_t)row * W + c], t);
         y[(size_t)row * W + c] = t;
     }
 }
@@ -1431,7 +1588,7 @@ static __global__ void ly_moe_accum_kernel(const float* __restrict__ ye, const i
                                            const float* __restrict__ sgate, int first, int W, float* __restrict__ y) {
     const int row = blockIdx.y;
     float w = 0.f;
-    if (e < 0) w = sgate[row];
+    if (e < 0) w = sgate ? sgate[row] : 1.f;
     else
         for (int k = 0; k < top; ++k) w += sel[row * top + k] == e ? wt[row * top + k] : 0.f;
     if (w == 0.f && !first) return;
@@ -1449,7 +1606,7 @@ static __global__ void ly_moe_combine_kernel(const float* __restrict__ eo, const
     for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < W; c += gridDim.x * blockDim.x) {
         float t = 0.f;
         for (int k = 0; k < top; ++k) t = fmaf(wt[row * top + k], eo[(size_t)pair_of[row * top + k] * W + c], t);
-        if (sh != nullptr) t = fmaf(sgate[row], sh[(size_t)row * W + c], t);
+        if (sh != nullptr) t = fmaf(sgate ? sgate[row] : 1.f, sh[(size_t)row * W + c], t);
         y[(size_t)row * W + c] = t;
     }
 }

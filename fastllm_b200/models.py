@@ -550,6 +550,12 @@ class _LayeredBase(_CausalBase):
     def stack_options(cls, config: dict, sc) -> None:
         """fills the stack-wide options of a FlStackConfig that the design reads from config.json (none by default)"""
 
+    @classmethod
+    def config_tensors(cls, config: dict):
+        """(name, f32 array) pairs the design states in config.json rather than in the checkpoint (per-head constants and the like);
+        they reach the device as tensors of those names, bit for bit"""
+        return ()
+
     def __init__(self, dev: DeviceModel, cfg, config: dict):
         super().__init__(dev, cfg)
         self.config = config
@@ -585,6 +591,8 @@ class _LayeredBase(_CausalBase):
                 if a.dtype.kind in "iu" and a.dtype != np.uint16:
                     continue            # integer tables: these designs read none
                 dev.put_tensor(name, a)
+        for name, arr in cls.config_tensors(config):
+            dev.put_tensor(name, np.ascontiguousarray(arr, dtype=np.float32))
         dev.finalize()
         self = cls(dev, sc, config)
         return self, cls.initialize_cache(device, dtype)
@@ -739,9 +747,96 @@ class TozaraxWithConfig(_LayeredBase):
         return min(self.KV_CAPACITY, int(self.config.get("max_positions") or self.KV_CAPACITY))
 
 
+def _rotary_bands_desc(d, rot: dict):
+    """rotary fields with Llama-3.1 style frequency scaling: 'scaling' = {factor, low, high, original}"""
+    d.rot_dims = int(rot.get("dims") or 0)
+    d.rot_base = float(rot.get("base", 10000.0))
+    sc = rot.get("scaling")
+    if sc:
+        d.rot_scaling = _lib.FL_ROT_SCALE["bands"]
+        d.yarn_factor, d.yarn_original = float(sc["factor"]), float(sc["original"])
+        d.yarn_fast, d.yarn_slow = float(sc["high"]), float(sc["low"])
+
+
+def _medulorn_softmax_desc(d, m: dict, windowed: bool):
+    """the two softmax attentions of the Medulorn decoder: chunk-masked with biased projections, per-head q/k norm and a sink of
+    score zero; or windowed with kept first tokens, q/k norm over the whole projection and a learned sink per head"""
+    d.mixer = _lib.FL_MIXER["attention"]
+    d.heads, d.dim, d.vdim = int(m["heads"]), int(m["dim"]), int(m["vdim"])
+    d.kv_heads, d.kv_from = int(m.get("kv_heads") or m["heads"]), -1
+    d.scale, d.rot_halves = float(m["scale"]), 1
+    mask = m.get("mask") or {}
+    if windowed:
+        d.window, d.keep_first = int(mask.get("size") or 0), int(mask.get("keep_first") or 0)
+        d.qk_norm_whole, d.sink = 1, 2
+    else:
+        d.mask_chunk = int(mask.get("size") or 0)
+        d.qkv_bias, d.sink = 1, 1
+    _rotary_bands_desc(d, m.get("rot") or {})
+
+
+def medulorn_layer_descs(config: dict):
+    """config.json of the Medulorn decoder -> ctypes array of FlLayerDesc: one descriptor for an 'attention' layer, two for a
+    'parallel' one (the windowed attention with the layer's feed-forward, then the lightning attention beside it).  Every size
+    and constant comes from the file."""
+    layers = config["layers"]
+    for i, l in enumerate(layers):
+        if l["type"] not in ("attention", "parallel"):
+            raise FastllmError(-1, f"layer {i}: unknown mixer type {l['type']!r}")
+    arr = (_lib.FlLayerDesc * sum(2 if l["type"] == "parallel" else 1 for l in layers))()
+    k = 0
+    for i, l in enumerate(layers):
+        a, m = arr[k], l["mixer"]
+        k += 1
+        if l["type"] == "attention":
+            _medulorn_softmax_desc(a, m, windowed=False)
+        else:
+            _medulorn_softmax_desc(a, m["left"], windowed=True)
+            a.beside, a.pair_sum, a.out_scale = 1, 1, float(m["left_scale"])
+            b, r = arr[k], m["right"]
+            k += 1
+            b.mixer, b.kv_from = _lib.FL_MIXER["lightning"], -1
+            b.heads, b.dim, b.vdim = int(r["heads"]), int(r["dim"]), int(r["vdim"])
+            b.out_scale = float(m["right_scale"])
+            if len(r["decay"]) != b.heads:
+                raise FastllmError(-1, f"layer {i}: one decay per head is needed")
+        mlp = l.get("mlp")
+        _ffn_desc(a, i, mlp, act="relu" if (mlp and mlp["kind"] == "dense") else "swish_clamp")
+        if a.ffn == _lib.FL_FFN["moe"]:
+            a.router_bias, a.shared_plain = 1, 1
+    return arr
+
+
+class MedulornWithConfig(_LayeredBase):
+    """The Medulorn decoder (no reference path): x <- norm(alpha x + sublayer(x)) with one number as every norm's weight; mixers read
+    x through a token shift; 'attention' layers (chunk mask, biased projections, sink of score zero) and 'parallel' layers (windowed
+    attention with kept first tokens and a learned sink, beside lightning attention, summed with fixed shares); a relu-gated dense
+    feed-forward or clamped-swish experts with a biased router and an ungated shared expert; scaled embedding, capped logits."""
+    arch, family, architectures = "medulorn", "Medulorn", ("Medulorn",)
+    norm_plain, no_pre_norm = True, True
+
+    @classmethod
+    def stack_options(cls, config: dict, sc) -> None:
+        sc.post_sum_norm, sc.residual_alpha = 1, float(config.get("postln_alpha", 1.0))
+        sc.norm_scalar, sc.token_shift = 1, 1
+        sc.embed_scale = float((config.get("embedding") or {}).get("scale") or 0.0)
+        sc.logit_softcap = float(config.get("logit_softcap") or 0.0)
+
+    @classmethod
+    def layer_descs(cls, config: dict, tensor_shapes: dict):
+        return medulorn_layer_descs(config)
+
+    @classmethod
+    def config_tensors(cls, config: dict):
+        for i, l in enumerate(config["layers"]):
+            if l["type"] == "parallel":
+                yield f"l{i}.mix.right.decay", np.asarray(l["mixer"]["right"]["decay"], dtype=np.float32)
+
+
 # every adapter, in the order the registry tries them (model_registry.rs:169-182 keeps the same kind of list)
 def registered_models():
-    return (LlamaWithConfig, MistralWithConfig, QwenWithConfig, MixtralWithConfig, NifunexWithConfig, RofetarWithConfig, TozaraxWithConfig)
+    return (LlamaWithConfig, MistralWithConfig, QwenWithConfig, MixtralWithConfig, NifunexWithConfig, RofetarWithConfig, TozaraxWithConfig,
+            MedulornWithConfig)
 
 
 def model_class_for(config: dict):

@@ -72,9 +72,13 @@ typedef enum fl_arch {
                               latent-attention mixers, dense / mixture-of-experts feed-forward, a norm before and after each sublayer */
     FL_ARCH_ROFETAR = 6,   /* layered decoder (no reference path): grouped-query attention with a softmax sink, Mamba-2 and gated-delta-rule
                               mixers, biased gelu feed-forward; only the OUTPUT of a sublayer is normed (fl_stack_config.no_pre_norm) */
-    FL_ARCH_TOZARAX = 7    /* layered decoder (no reference path): learned positions; pre-normed sublayers that read their input through a
+    FL_ARCH_TOZARAX = 7,   /* layered decoder (no reference path): learned positions; pre-normed sublayers that read their input through a
                               short causal convolution, gate their contribution and average over all earlier layers' outputs; two mixers
                               side by side (windowed attention without rotation | gated delta rule); sigmoid-routed squared-relu experts */
+    FL_ARCH_MEDULORN = 8   /* layered decoder (no reference path): x <- norm(alpha x + sub(x)) with one number as the norm's weight
+                              (fl_stack_config.post_sum_norm); mixers read x through a token shift; chunk-masked attention with biased
+                              projections | sliding-window attention with kept first tokens and a learned sink beside lightning attention;
+                              relu-gated dense feed-forward or clamped-swish experts with a biased router; scaled embedding, capped logits */
 } fl_arch;
 
 typedef enum fl_dtype { FL_DTYPE_F32 = 0, FL_DTYPE_BF16 = 1, FL_DTYPE_F16 = 2 } fl_dtype;
@@ -140,10 +144,25 @@ typedef struct fl_config {
  * scores stay eligible, the `top` eligible experts with the largest choice scores are used with weights s (not renormalised).
  * Two mixers side by side (`beside`): both read the layer's mixer input; the layer's mixer output is half the sum of the two
  * outputs, each RMS-normed over the width with a plain weight ("l<i>.mix.left.out" / "l<i>.mix.right.out"); their tensors are
- * "l<i>.mix.left.*" / "l<i>.mix.right.*". */
-typedef enum fl_mixer_kind { FL_MIXER_GLA = 0, FL_MIXER_LATENT_ATTN = 1, FL_MIXER_ATTN = 2, FL_MIXER_MAMBA2 = 3, FL_MIXER_DELTA = 4 } fl_mixer_kind;
+ * "l<i>.mix.left.*" / "l<i>.mix.right.*"; with `pair_sum` the output is out_scale_left * left + out_scale_right * right instead and
+ * no such weights exist.
+ *   FL_MIXER_LIGHTNING    lightning attention: q = silu(W_q h), k = silu(W_k h) (heads x dim), v = silu(W_v h) (heads x vdim); per head an
+ *                         f32 state S [dim, vdim]: S <- decay_h S + k v^T, o = S^T q with one fixed decay per head (tensor "decay"
+ *                         [heads], kept in f32 as given); the concatenated heads are RMS-normed together (plain weight "norm"
+ *                         [heads * vdim]), multiplied by sigmoid(W_g h) and projected.
+ * Attention masks: `window` (i - j < window), `keep_first` (keys j < keep_first stay visible whatever the window; they keep their own
+ * positions) and `mask_chunk` (i and j must lie in the same block of mask_chunk positions counted from the sequence's start) combine:
+ * j <= i is visible iff it passes the chunk rule and (the window rule or the kept-first rule).  sink = 2: the softmax denominator
+ * gains exp(s_h) with a learned s_h per query head (tensor "sink" [heads], not scaled).  qkv_bias: "q.b" / "k.b" / "v.b" are added
+ * to the projections.  qk_norm_whole: the q (and k) norm runs over all heads' channels at once with a weight of that length.
+ * rot_scaling = FL_ROT_SCALE_BANDS: frequencies whose wavelength is below yarn_original / yarn_fast stay, above yarn_original /
+ * yarn_slow are divided by yarn_factor, between the two blend linearly in yarn_original / wavelength; cos and sin keep magnitude 1.
+ * Feed-forward (ffn_act = FL_ACT_RELU): y = W_down (relu(W_gate h) * (W_up h)).  router_bias: "mlp.router.b" is added to the router
+ * logits.  shared_plain: the shared expert's output is added as it is (no "mlp.shared.sg"). */
+typedef enum fl_mixer_kind { FL_MIXER_GLA = 0, FL_MIXER_LATENT_ATTN = 1, FL_MIXER_ATTN = 2, FL_MIXER_MAMBA2 = 3, FL_MIXER_DELTA = 4, FL_MIXER_LIGHTNING = 5 } fl_mixer_kind;
 typedef enum fl_ffn_kind { FL_FFN_NONE = 0, FL_FFN_DENSE = 1, FL_FFN_MOE = 2 } fl_ffn_kind;
-typedef enum fl_ffn_act { FL_ACT_SWISH_CLAMP = 0, FL_ACT_GELU_TANH = 1, FL_ACT_RELU2 = 2 } fl_ffn_act;
+typedef enum fl_ffn_act { FL_ACT_SWISH_CLAMP = 0, FL_ACT_GELU_TANH = 1, FL_ACT_RELU2 = 2, FL_ACT_RELU = 3 } fl_ffn_act;
+typedef enum fl_rot_scaling { FL_ROT_SCALE_YARN = 0, FL_ROT_SCALE_BANDS = 1 } fl_rot_scaling;
 typedef enum fl_router_kind { FL_ROUTER_SOFTMAX = 0, FL_ROUTER_SIGMOID_GROUPS = 1 } fl_router_kind;
 
 typedef struct fl_layer_desc {
@@ -169,7 +188,7 @@ typedef struct fl_layer_desc {
     int32_t conv;                      /* Mamba-2 / delta rule: taps of the short causal convolution */
     int32_t state, groups, norm_groups;/* Mamba-2: state size per head, B / C groups, parts of the gated output norm */
     float softcap;                     /* attention: score <- softcap * tanh(score / softcap); 0 = none */
-    int32_t sink;                      /* attention: 1 = one is added to the softmax denominator */
+    int32_t sink;                      /* attention: 1 = one is added to the softmax denominator; 2 = exp(sink_h), a learned number per head */
     int32_t rot_halves;                /* attention: 1 = rotary pairs are (i, i + rot_dims / 2), 0 = (2i, 2i + 1) */
     int32_t ffn_act, ffn_bias;         /* feed-forward: fl_ffn_act; dense: 1 = gate / up / down carry biases */
     int32_t no_qk_norm;                /* attention: 1 = queries and keys are used as projected (no per-head norm, no norm tensors) */
@@ -177,7 +196,16 @@ typedef struct fl_layer_desc {
                                           it counts as no layer of its own); attention or delta rule, each with its own cache / state */
     int32_t router;                    /* MoE: fl_router_kind */
     int32_t route_groups, route_keep;  /* FL_ROUTER_SIGMOID_GROUPS: groups of neighbouring experts / groups that stay eligible */
-    int32_t reserved[1];
+    int32_t qkv_bias;                  /* attention: 1 = the q, k and v projections carry biases */
+    int32_t qk_norm_whole;             /* attention: 1 = q and k are normed over all their heads' channels at once (weights of that length) */
+    int32_t mask_chunk;                /* attention: > 0 = a position sees only the keys of its own block of this many positions */
+    int32_t keep_first;                /* attention with a window: the first keep_first keys of the sequence stay visible */
+    int32_t rot_scaling;               /* fl_rot_scaling: how yarn_factor / yarn_original / yarn_fast / yarn_slow change the frequencies */
+    float out_scale;                   /* mixers side by side with pair_sum: this mixer's share of the sum */
+    int32_t pair_sum;                  /* beside: 1 = the layer's mixer output is the out_scale-weighted sum of the two mixers' outputs */
+    int32_t router_bias;               /* MoE, FL_ROUTER_SOFTMAX: 1 = the router logits carry a bias */
+    int32_t shared_plain;              /* MoE: 1 = the shared expert is not gated */
+    int32_t reserved[2];
 } fl_layer_desc;
 
 typedef struct fl_stack_config {
@@ -198,6 +226,14 @@ typedef struct fl_stack_config {
                                           h = the sublayer's normed input before the convolution */
     int32_t depth_avg;                 /* 1: what leaves layer i is sum_j dwa[j] X_j over X_0 = the embedding output and X_j+1 = layer j's own
                                           result, j <= i ("l<i>.dwa" [i + 2]) */
+    int32_t post_sum_norm;             /* 1: x <- norm(residual_alpha x + sub(x)) -- the norm follows the sum (needs no_pre_norm; "l<i>.norm1" /
+                                          "norm2" name these norms) */
+    float residual_alpha;
+    int32_t norm_scalar;               /* 1: every layer norm and the final norm has ONE number as its weight (a tensor of one element) */
+    float embed_scale;                 /* != 0: the embedding row is multiplied by this */
+    float logit_softcap;               /* > 0: logits <- cap tanh(logits / cap) */
+    int32_t token_shift;               /* 1: a mixer reads h + (h_prev - h) * shift, h_prev = the previous token's mixer input of the same layer
+                                          before this replacement, zeros at position 0 ("l<i>.shift" [width]); h_prev is kept per slot and layer */
     int32_t reserved[3];
 } fl_stack_config;
 

@@ -39,9 +39,9 @@ def test_config_to_layer_descs():
 
 def test_descriptor_layout_matches_header():
     """the two structs as the header lays them out (4-byte fields, one double aligned to 8)"""
-    assert ctypes.sizeof(_lib.FlStackConfig) == 16 * 4
+    assert ctypes.sizeof(_lib.FlStackConfig) == 22 * 4
     assert _lib.FlLayerDesc.rot_base.offset == 48 and _lib.FlLayerDesc.kv_heads.offset == 104
-    assert ctypes.sizeof(_lib.FlLayerDesc) == 104 + 16 * 4
+    assert ctypes.sizeof(_lib.FlLayerDesc) == 104 + 26 * 4
 
 
 def test_registry_picks_by_architecture():

@@ -48,9 +48,9 @@ def test_config_to_layer_descs_and_stack_options():
 def test_descriptor_layout_matches_header():
     """the new fields sit where the header puts them (4-byte fields behind ffn_bias; the stack options behind no_pre_norm)"""
     assert _lib.FlLayerDesc.no_qk_norm.offset == 104 + 10 * 4 and _lib.FlLayerDesc.route_keep.offset == 104 + 14 * 4
-    assert ctypes.sizeof(_lib.FlLayerDesc) == 104 + 16 * 4
+    assert ctypes.sizeof(_lib.FlLayerDesc) == 104 + 26 * 4
     assert _lib.FlStackConfig.no_post_norm.offset == 8 * 4 and _lib.FlStackConfig.depth_avg.offset == 12 * 4
-    assert ctypes.sizeof(_lib.FlStackConfig) == 16 * 4
+    assert ctypes.sizeof(_lib.FlStackConfig) == 22 * 4
 
 
 def test_registry_picks_by_architecture():
