@@ -249,9 +249,10 @@ class Medulorn:
 # ---- random models for tests -----------------------------------------------------------------------------------------
 def to_bf16(a):
     """round-to-nearest-even to bfloat16, returned as float32"""
-    b = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    shape = np.shape(a)
+    b = np.ascontiguousarray(a, dtype=np.float32).reshape(-1).view(np.uint32)
     r = ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint32) << 16
-    return r.view(np.float32)
+    return r.view(np.float32).reshape(shape)
 
 
 def tensor_shapes(cfg: dict) -> dict:
