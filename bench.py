@@ -59,6 +59,11 @@ WORKLOADS = {
                            "squared-relu experts, input convolutions, gated contributions, depth average) beside Rofetar (attention / delta rule "
                            "layers alternating, dense feed-forward of the two chosen experts' width) and Nifunex (softmax-routed experts) at equal "
                            "width / layers: 2048-token prefill and batch-8 decode at 2k context, random weights"),
+    "medulorn_vs_tozarax": ("medulorn", 8, 2048, "layered decoder (Medulorn: norm of the sum, token shift; windowed attention with kept first tokens "
+                            "and a learned sink beside lightning attention, alternating with chunk-masked attention; clamped-swish experts with a "
+                            "shared expert) beside Tozarax (attention beside a delta rule in every layer, experts) and Rofetar (attention with q/k "
+                            "norm, rotation and sink / delta rule alternating, dense feed-forward) at equal width / layers: 2048-token prefill and "
+                            "batch-8 decode at 2k context, random weights"),
 }
 QWEN_PREFILL_TFLOP_4K = 56.83         # 53.46 linear + 3.37 causal attention
 MINILM_FLOP_PER_TOKEN = 22.41e6      # 2 x 10.617 M linear + 4 T H 6 attention at T = 128
@@ -352,7 +357,7 @@ def run_reference(args, rank):
     if rank != 0:
         return
     arch, batch, ctx, desc = WORKLOADS[args.workload]
-    if args.workload in ("mixtral8x7b_b32", "qwen25_7b_prefill4k", "nifunex_vs_mixtral", "rofetar_vs_nifunex", "tozarax_vs_rofetar"):
+    if args.workload in ("mixtral8x7b_b32", "qwen25_7b_prefill4k", "nifunex_vs_mixtral", "rofetar_vs_nifunex", "tozarax_vs_rofetar", "medulorn_vs_tozarax"):
         print(json.dumps({"impl": "reference", "unavailable": f"no CPU leg for workload {args.workload}: the reference does not wire Mixtral "
                           "and a 4096-token f32 prefill of a 7B model does not fit a bounded CPU sample; the decode workloads carry the CPU baseline"}),
               flush=True)
@@ -1178,6 +1183,90 @@ def run_tozarax_compare(args, local_rank):
                       "clocks": clk.summary(t_wall0, t_wall1), "sizes": results}), flush=True)
 
 
+def _medulorn_config(width, ff, layers, vocab, window=1024, chunk=8192):
+    """A Medulorn config at the sizes of a real model's layers: heads of 128 channels; even layers run a windowed attention (4 query
+    heads per key/value head, 1024 keys + 4 kept first ones, banded rotary scaling) beside lightning attention (as many heads of
+    128 x 128), odd layers a chunk-masked attention; 8 clamped-swish experts of hidden width ff, top 2, plus a shared expert."""
+    H = width // 128
+    rot = {"base": 500000.0, "dims": 128}
+    ly = []
+    for i in range(layers):
+        mlp = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": 8, "top": 2}, "shared": {"ff": ff, "limit": 7.0}}
+        if i % 2 == 0:
+            left = {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window, "keep_first": 4},
+                    "rot": dict(rot, scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192})}
+            right = {"heads": H, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 5 * h / max(1, H - 1)) for h in range(H)]}
+            ly.append({"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.5, "right_scale": 0.5}, "mlp": mlp})
+        else:
+            ly.append({"type": "attention", "mixer": {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                                      "mask": {"size": chunk}, "rot": rot}, "mlp": mlp})
+    return {"architecture": "Medulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "postln_alpha": 1.0, "embedding": {"scale": 1.0},
+            "logit_softcap": 30.0, "layers": ly}
+
+
+def run_medulorn_compare(args, local_rank):
+    """--workload medulorn_vs_tozarax (one GPU): Medulorn beside the two closest existing designs at the same width / layer count,
+    random weights -- Tozarax (two mixers side by side on the same attention and scan kernels, experts on the same grouped GEMMs) and
+    Rofetar (attention with q/k norm, rotation and sink).  One 2048-token prefill and batch-8 decode steps at a 2k context, through
+    the public calls (host ids in, logits out), with the per-kernel CUDA-event profile of one call of each kind."""
+    import torch
+    from fastllm_b200 import models
+    batch, T, steps, warm = 8, 2048, max(4, min(args.steps, 32)), 3
+    sizes = [("w1024", 1024, 1408, 4), ("w2048", 2048, 2816, 4), ("w4096", 4096, 7168, 4)]
+    vocab = 32000
+    results = {}
+
+    def timed(fn, n):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / n
+
+    def layered(cls, cfg, **hints):
+        model, _ = cls.initialize_model(cfg, None, "bf16", local_rank, random_seed=0, std=0.02, **hints)
+        cache = model.new_device_cache(max_batch=batch, max_seq=T + 64, pool_tokens=batch * (T + 64))
+        ids = (np.arange(T, dtype=np.uint64) * 7919 % (vocab - 5) + 3).astype(np.uint32)
+
+        def prefill():
+            cache.slot_reset(0)
+            cache.forward_ragged([0], [ids], None)
+        dt_p = timed(prefill, max(2, steps // 4))
+        models.prof_begin(); prefill(); prof_p = models.prof_end()
+        for s in range(1, batch):
+            cache.forward_ragged([s], [ids], None)
+        slots = list(range(batch))
+
+        def decode():
+            cache.forward_ragged(slots, [[7 + s] for s in slots], None)
+        dt_d = timed(decode, steps)
+        models.prof_begin(); decode(); prof_d = models.prof_end()
+        return {"prefill_tok_s": T / dt_p, "prefill_ms": dt_p * 1e3, "decode_tok_s": batch / dt_d, "decode_ms_per_step": dt_d * 1e3,
+                "weight_bytes": model.dev.streamed_bytes(), "prefill_kernels": _profile_table(prof_p), "decode_kernels": _profile_table(prof_d)}
+
+    with ClockSampler(local_rank) as clk:
+        t_wall0 = time.time()
+        for name, width, ff, layers in sizes:
+            rec = {"width": width, "expert_ff": ff, "layers": layers}
+            rec["medulorn"] = layered(models.MedulornWithConfig, _medulorn_config(width, ff, layers, vocab))
+            rec["tozarax"] = layered(models.TozaraxWithConfig, _tozarax_config(width, ff, layers, vocab))
+            rec["rofetar"] = layered(models.RofetarWithConfig, _rofetar_pair_config(width, ff, layers, vocab))
+            results[name] = rec
+        t_wall1 = time.time()
+        time.sleep(0.12)
+    big = results[sizes[-1][0]]
+    print(json.dumps({"metric": "decode_tokens_per_s", "value": big["medulorn"]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
+                      "ms_per_step": big["medulorn"]["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                      "data": "synthetic",
+                      "config": {"workload": WORKLOADS[args.workload][3], "batch": batch, "context": T, "timing": "wall clock around the public call "
+                                 "(host ids in, f32 logits out) with a device synchronise on both sides; per-kernel figures are CUDA events",
+                                 "l2": "weights of a step exceed L2 at every size"},
+                      "clocks": clk.summary(t_wall0, t_wall1), "sizes": results}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1214,6 +1303,9 @@ def main():
     elif args.workload == "tozarax_vs_rofetar":
         if rank == 0:
             run_tozarax_compare(args, local_rank)
+    elif args.workload == "medulorn_vs_tozarax":
+        if rank == 0:
+            run_medulorn_compare(args, local_rank)
     elif args.workload == "rofetar_vs_nifunex":
         if rank == 0:
             run_rofetar_compare(args, local_rank)

@@ -1034,9 +1034,12 @@ static void run_mixer(fl_cache& c, LaunchCtx& lc, const StepTab& st, const Layer
         AttnPrepArgs pa{y.proj.p, lw.n_in, lw.off_q, lw.off_k, lw.off_v, lw.qnorm, lw.knorm, eps, y.kv_pool[lw.kv_index], y.page_table.p,
                         c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot, y.rope_cos[lw.rope_index].p, y.rope_sin[lw.rope_index].p,
                         H, G, D, Dv, d.rot_dims, d.rot_halves, lw.bq, lw.bk, lw.bv, d.qk_norm_whole};
-        const size_t psm = (size_t)4 * D * 4;
-        if (m.f32) launch(lc, "attn_prep", 0, ly_attn_prep_kernel<float>, dim3(Ti), dim3(128), psm, pa);
-        else launch(lc, "attn_prep", 0, ly_attn_prep_kernel<uint16_t>, dim3(Ti), dim3(128), psm, pa);
+        // eight warps per block take the heads in turn; steps of few rows spread a row's heads over up to four blocks (not with a
+        // norm over the whole projection: its sums read every head before any is rewritten in place, which one block orders)
+        const size_t psm = (size_t)8 * D * 4;
+        const int heads_all = H + (lw.off_k >= 0 ? G : 0), py = (Ti <= 64 && !d.qk_norm_whole) ? std::max(1, std::min(4, (heads_all + 7) / 8)) : 1;
+        if (m.f32) launch(lc, "attn_prep", 0, ly_attn_prep_kernel<float>, dim3(Ti, py), dim3(256), psm, pa);
+        else launch(lc, "attn_prep", 0, ly_attn_prep_kernel<uint16_t>, dim3(Ti, py), dim3(256), psm, pa);
         GqaAttnArgs at{y.proj.p, lw.n_in, lw.off_q, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot,
                        y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo, H, G, D, Dv, d.window, d.scale, d.softcap, d.sink, 0, y.at_part.p,
                        d.keep_first, d.mask_chunk, lw.sinkv};

@@ -789,31 +789,25 @@ struct AttnPrepArgs {
 };
 // Per row: every query head and (when the layer owns its cache) every key head is RMS-normed over dim with a weight shared by the
 // heads (qnorm == nullptr: they are used as projected), then its first rdims channels are turned by the row's position: pairs (i, i + rdims/2) when `halves`, else (2i, 2i+1).
-// Queries are rewritten in place, keys and values go to the row's cache page.  One warp per head in turn.  Biases, when the
-// projections have them, are added first (in place); with `whole` the mean square is taken over all heads of q (of k) and the weight
-// is indexed by the channel inside the whole projection.
+// Queries are rewritten in place, keys and values go to the row's cache page.  grid (rows, head chunks): the warps of a row's blocks
+// take the heads in turn.  Biases, when the projections have them, are added as the values are read; with `whole` the mean square is
+// taken over all heads of q (of k) before any head is rewritten (one block per row then: gridDim.y = 1) and the weight is indexed by
+// the channel inside the whole projection.
 template <typename CT>
-static __global__ void __launch_bounds__(128) ly_attn_prep_kernel(AttnPrepArgs a) {
-    extern __shared__ float sm[];               // [4 warps][D]
+static __global__ void __launch_bounds__(256) ly_attn_prep_kernel(AttnPrepArgs a) {
+    extern __shared__ float sm[];               // [warps][D]
     __shared__ float red[33];
-    const int row = blockIdx.x, pos = a.row_pos[row], lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int row = blockIdx.x, pos = a.row_pos[row], lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float* pr = a.proj + (size_t)row * a.ldp;
-    if (a.bq != nullptr) {
-        for (int c = threadIdx.x; c < a.H * a.D; c += blockDim.x) pr[a.off_q + c] += a.bq[c];
-        if (a.off_k >= 0) {
-            for (int c = threadIdx.x; c < a.G * a.D; c += blockDim.x) pr[a.off_k + c] += a.bk[c];
-            for (int c = threadIdx.x; c < a.G * a.Dv; c += blockDim.x) pr[a.off_v + c] += a.bv[c];
-        }
-        __syncthreads();
-    }
+    const bool own = a.off_k >= 0;
     float rq = 0.f, rk = 0.f;
     if (a.whole && a.qnorm != nullptr) {
         float ss = 0.f;
-        for (int c = threadIdx.x; c < a.H * a.D; c += blockDim.x) ss += pr[a.off_q + c] * pr[a.off_q + c];
+        for (int c = threadIdx.x; c < a.H * a.D; c += blockDim.x) { const float v = pr[a.off_q + c] + (a.bq ? a.bq[c] : 0.f); ss += v * v; }
         rq = 1.f / sqrtf(block_sum(ss, red) / (float)(a.H * a.D) + a.eps);
-        if (a.off_k >= 0) {
+        if (own) {
             ss = 0.f;
-            for (int c = threadIdx.x; c < a.G * a.D; c += blockDim.x) ss += pr[a.off_k + c] * pr[a.off_k + c];
+            for (int c = threadIdx.x; c < a.G * a.D; c += blockDim.x) { const float v = pr[a.off_k + c] + (a.bk ? a.bk[c] : 0.f); ss += v * v; }
             rk = 1.f / sqrtf(block_sum(ss, red) / (float)(a.G * a.D) + a.eps);
         }
     }
@@ -821,7 +815,6 @@ static __global__ void __launch_bounds__(128) ly_attn_prep_kernel(AttnPrepArgs a
     const float* cs = a.cosb + (size_t)pos * half;
     const float* sn = a.sinb + (size_t)pos * half;
     float* buf = sm + wid * a.D;
-    const bool own = a.off_k >= 0;
     CT* dst = nullptr;
     if (own) {
         const int slot = a.seq_slot[a.row_seq[row]];
@@ -829,23 +822,28 @@ static __global__ void __launch_bounds__(128) ly_attn_prep_kernel(AttnPrepArgs a
         dst = (CT*)a.pool + ((size_t)page * kKvPage + pos % kKvPage) * ((size_t)a.G * (a.D + a.Dv));
     }
     const int items = a.H + (own ? a.G : 0);
-    for (int it = wid; it < items; it += 4) {
+    for (int it = blockIdx.y * nw + wid; it < items; it += gridDim.y * nw) {
         const bool isq = it < a.H;
-        float* src = isq ? pr + a.off_q + it * a.D : pr + a.off_k + (it - a.H) * a.D;
+        const int hd = isq ? it : it - a.H;
+        float* src = isq ? pr + a.off_q + hd * a.D : pr + a.off_k + hd * a.D;
+        const float* bias = isq ? a.bq : a.bk;
+        if (bias != nullptr) bias += (size_t)hd * a.D;
         const float* w = isq ? a.qnorm : a.knorm;
-        if (w != nullptr && a.whole) {
-            const float r = isq ? rq : rk;
-            w += (size_t)(isq ? it : it - a.H) * a.D;
-            for (int c = lane; c < a.D; c += 32) buf[c] = src[c] * r * w[c];
-        } else if (w != nullptr) {
-            float ss = 0.f;
-            for (int c = lane; c < a.D; c += 32) ss += src[c] * src[c];
-            const float r = 1.f / sqrtf(warp_sum(ss) / (float)a.D + a.eps);
-            for (int c = lane; c < a.D; c += 32) buf[c] = src[c] * r * w[c];
-        } else {
-            for (int c = lane; c < a.D; c += 32) buf[c] = src[c];
-        }
+        for (int c = lane; c < a.D; c += 32) buf[c] = src[c] + (bias ? bias[c] : 0.f);
         __syncwarp();
+        if (w != nullptr) {
+            float r;
+            if (a.whole) {
+                r = isq ? rq : rk;
+                w += (size_t)hd * a.D;
+            } else {
+                float ss = 0.f;
+                for (int c = lane; c < a.D; c += 32) ss += buf[c] * buf[c];
+                r = 1.f / sqrtf(warp_sum(ss) / (float)a.D + a.eps);
+            }
+            for (int c = lane; c < a.D; c += 32) buf[c] = buf[c] * r * w[c];
+            __syncwarp();
+        }
         for (int c = lane; c < a.D; c += 32) {
             float val = buf[c];
             if (c < a.rdims) {
@@ -856,14 +854,14 @@ static __global__ void __launch_bounds__(128) ly_attn_prep_kernel(AttnPrepArgs a
                 const float u = buf[cu], v = buf[cv];
                 val = second ? v * cs[pi] + u * sn[pi] : u * cs[pi] - v * sn[pi];
             }
-            if (isq) src[c] = val; else st_c(dst + (size_t)(it - a.H) * a.D + c, val);
+            if (isq) src[c] = val; else st_c(dst + (size_t)hd * a.D + c, val);
         }
         __syncwarp();
     }
-    if (own) {
+    if (own && blockIdx.y == 0) {
         const float* v = pr + a.off_v;
         CT* vd = dst + (size_t)a.G * a.D;
-        for (int c = threadIdx.x; c < a.G * a.Dv; c += blockDim.x) st_c(vd + c, v[c]);
+        for (int c = threadIdx.x; c < a.G * a.Dv; c += blockDim.x) st_c(vd + c, v[c] + (a.bv ? a.bv[c] : 0.f));
     }
 }
 
