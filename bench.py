@@ -1201,7 +1201,7 @@ def _medulorn_config(width, ff, layers, vocab, window=1024, chunk=8192):
             ly.append({"type": "attention", "mixer": {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
                                                       "mask": {"size": chunk}, "rot": rot}, "mlp": mlp})
     return {"architecture": "Medulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "postln_alpha": 1.0, "embedding": {"scale": 1.0},
-            "logit_softcap": 30.0, "layers": ly}
+            "logit_softcap": 50.0, "layers": ly}
 
 
 def run_medulorn_compare(args, local_rank):

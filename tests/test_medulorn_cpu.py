@@ -15,7 +15,7 @@ def _cfg():
             "logit_softcap": 12.0, "layers": [
         {"type": "attention",
          "mixer": {"heads": 6, "kv_heads": 3, "dim": 8, "vdim": 10, "scale": 0.3, "mask": {"size": 17}, "rot": {"dims": 6, "base": 777.0}},
-         "mlp": {"kind": "moe", "expert": {"ff": 14, "limit": 0.75}, "router": {"experts": 12, "top": 3}, "shared": {"ff": 9, "limit": 2.5}}},
+         "mlp": {"kind": "moe", "expert": {"ff": 14, "limit": 0.75}, "router": {"experts": 10, "top": 3}, "shared": {"ff": 9, "limit": 2.5}}},
         {"type": "parallel",
          "mixer": {"left": {"heads": 2, "kv_heads": 1, "dim": 4, "vdim": 6, "scale": 0.5, "mask": {"size": 3, "keep_first": 2},
                             "rot": {"dims": 4, "base": 100.0, "scaling": {"factor": 2.0, "low": 1.0, "high": 8.0, "original": 64}}},
@@ -33,7 +33,7 @@ def test_config_to_layer_descs_and_stack_options():
     assert (a.mask_chunk, a.window, a.keep_first, a.qkv_bias, a.qk_norm_whole, a.sink, a.no_qk_norm) == (17, 0, 0, 1, 0, 1, 0)
     assert (a.rot_dims, a.rot_base, a.rot_halves, a.yarn_factor) == (6, 777.0, 1, 0.0) and abs(a.scale - 0.3) < 1e-7
     assert (a.ffn, a.ffn_act, a.ff, a.experts, a.top, a.router, a.router_bias, a.shared_ff, a.shared_plain) == \
-        (_lib.FL_FFN["moe"], _lib.FL_ACT["swish_clamp"], 14, 12, 3, _lib.FL_ROUTER["softmax"], 1, 9, 1)
+        (_lib.FL_FFN["moe"], _lib.FL_ACT["swish_clamp"], 14, 10, 3, _lib.FL_ROUTER["softmax"], 1, 9, 1)
     assert (a.limit, a.shared_limit) == (0.75, 2.5)
     assert (b.mixer, b.window, b.keep_first, b.mask_chunk, b.qkv_bias, b.qk_norm_whole, b.sink, b.beside, b.pair_sum) == \
         (_lib.FL_MIXER["attention"], 3, 2, 0, 0, 1, 2, 1, 1)
@@ -150,7 +150,7 @@ def test_router_and_experts():
 def test_model_shape_and_the_norm_of_the_sum():
     cfg = _cfg()
     w = O.random_weights(cfg, 3)
-    assert set(w) == set(O.tensor_shapes(cfg)) and "l2.norm2" not in w and "l1.mix.right.decay" not in w and "l0.mlp.e11.down" in w
+    assert set(w) == set(O.tensor_shapes(cfg)) and "l2.norm2" not in w and "l1.mix.right.decay" not in w and "l0.mlp.e9.down" in w
     assert w["l0.norm1"].shape == () and w["l1.mix.left.q.norm"].shape == (8,) and w["l0.mix.q.norm"].shape == (8,) and w["l1.mix.left.sink"].shape == (2,)
     m = O.Medulorn(cfg, w)
     lg, tr = m.run([1, 2, 3, 4, 5, 6], layer_trace=True)
