@@ -541,6 +541,12 @@ void layered_finalize(LayeredModel& m) {
         }
         map(m.head, m.V, m.W, m.tm_head, m.tc_head);
     }
+    // the norm of the sum parks a row in shared memory: above the default 48 KB the kernels are told so once
+    if (m.cfg.post_sum_norm && (size_t)m.W * 4 > 48 * 1024) {
+        FL_CHECK((size_t)m.W * 4 <= 200 * 1024, FL_ERR_UNSUPPORTED, "a norm of the sum is built for widths up to 51200");
+        FL_CUDA(cudaFuncSetAttribute(ly_sum_norm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, m.W * 4));
+        FL_CUDA(cudaFuncSetAttribute(ly_sum_norm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, m.W * 4));
+    }
     m.finalized = true;
 }
 
@@ -1108,7 +1114,8 @@ static void run_mixer(fl_cache& c, LaunchCtx& lc, const StepTab& st, const Layer
         RecArgs ra{y.cv.p, lw.conv_ch, lw.off_q - lw.conv_off, lw.off_k - lw.conv_off, lw.off_v - lw.conv_off, y.rs.p, (const float*)nullptr, y.go.p,
                    y.gla_state[lw.gla_index].p, st.seq_row0, st.seq_slot, st.seq_pos0, H, H, D, Dv};
         launch_rec_scan<false>(lc, ra, n);
-        launch(lc, "gated_group_norm", 0, ly_gated_group_norm_kernel, dim3(Ti, 1), dim3(std::min(1024, std::max(64, (inner + 31) / 32 * 32))), 0,
+        const bool v4 = ((inner | lw.n_in | lw.off_g) & 3) == 0;       // four channels per thread
+        launch(lc, "gated_group_norm", 0, ly_gated_group_norm_kernel, dim3(Ti, 1), dim3(std::min(v4 ? 256 : 1024, std::max(64, ((v4 ? inner / 4 : inner) + 31) / 32 * 32))), 0,
                (const float*)y.go.p, (const float*)y.proj.p, lw.n_in, lw.off_g, (const float*)lw.hnorm, eps, inner, 1, 1, y.u.p,
                lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
     } else if (d.mixer == FL_MIXER_GLA) {

@@ -1126,7 +1126,17 @@ static __global__ void ly_lightning_prep_kernel(const float* __restrict__ proj, 
                                                 float* __restrict__ cv, float* __restrict__ ab) {
     const int row = blockIdx.x, c0 = blockIdx.y * chunk, c1 = min(ch, c0 + chunk);
     const float* pr = proj + (size_t)row * ldp + off;
-    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) cv[(size_t)row * ch + c] = siluf_(pr[c]);
+    if (((ldp | off | ch | chunk) & 3) == 0) {          // 16-byte rows: four channels per thread
+        for (int c = c0 + threadIdx.x * 4; c < c1; c += blockDim.x * 4) {
+            float t[4];
+            ld_vec<4>(pr + c, t);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) t[i] = siluf_(t[i]);
+            st_vec<4>(cv + (size_t)row * ch + c, t);
+        }
+    } else {
+        for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) cv[(size_t)row * ch + c] = siluf_(pr[c]);
+    }
     if (blockIdx.y != 0) return;
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
         ab[((size_t)row * H + h) * 2] = decay[h];
@@ -1351,6 +1361,30 @@ static __global__ void ly_gated_group_norm_kernel(const float* __restrict__ y, c
     const int row = blockIdx.x, n = inner / parts, c0 = blockIdx.y * n;
     const float* yr = y + (size_t)row * inner + c0;
     const float* zr = proj + (size_t)row * ldp + off_z + c0;
+    if (((inner | n | ldp | off_z) & 3) == 0) {         // 16-byte rows and parts: four channels per thread
+        float ss = 0.f;
+        for (int c = threadIdx.x * 4; c < n; c += blockDim.x * 4) {
+            float a[4], z[4];
+            ld_vec<4>(yr + c, a);
+            if (!sig_after) {
+                ld_vec<4>(zr + c, z);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) a[i] *= siluf_(z[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ss += a[i] * a[i];
+        }
+        const float r = 1.f / sqrtf(block_sum(ss, red) / (float)n + eps);
+        for (int c = threadIdx.x * 4; c < n; c += blockDim.x * 4) {
+            float a[4], z[4], ww[4];
+            ld_vec<4>(yr + c, a); ld_vec<4>(zr + c, z); ld_vec<4>(w + c0 + c, ww);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = sig_after ? a[i] * r * ww[i] * sigmoidf_(z[i]) : a[i] * siluf_(z[i]) * r * ww[i];
+            st_vec<4>(u + (size_t)row * inner + c0 + c, a);
+            split_store_vec<4>(uhi, ulo, (size_t)row * inner + c0 + c, a);
+        }
+        return;
+    }
     float ss = 0.f;
     for (int c = threadIdx.x; c < n; c += blockDim.x) { const float v = sig_after ? yr[c] : yr[c] * siluf_(zr[c]); ss += v * v; }
     const float r = 1.f / sqrtf(block_sum(ss, red) / (float)n + eps);
